@@ -1,0 +1,260 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the engine at Qwen3-8B layer sizes with random weights.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl reference]
+
+One JSON line on stdout.  `value` is decoded tokens a second at batch 8 with 2,048 cached tokens
+per sequence (a step = one decode step of the whole batch), timed on the device with the sampler's
+tokens fed back on the device; `e2e` is the same through `LanguageModel.generate` with host token
+ids in and out every step.  `prefill` is one 2,048-token prompt, `points` decoding at batch 1 and
+64, `roofline` the bytes a decode step has to read (every weight once, the cache of the live
+requests) over its time against the measured copy bandwidth.
+
+The library runs on one GPU: for --gpus > 1 a line says so and the exit code is 2.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# layer sizes of the benchmark configuration (Qwen3-8B): 36 layers of hidden 4096, 32 query and 8
+# key/value heads of 128, feed-forward 12288, vocabulary 151936, separate head
+QWEN3_8B = dict(hidden_size=4096, num_hidden_layers=36, num_attention_heads=32, num_key_value_heads=8,
+                head_dim=128, intermediate_size=12288, vocab_size=151936, rope_theta=1e6, rms_norm_eps=1e-6,
+                max_position_embeddings=40960, tie_word_embeddings=False)
+CONTEXT = 4096          # tokens per sequence the benchmark's context allows
+CACHED = 2048           # tokens each sequence holds when decoding is timed
+PREFILL_TOKENS = 2048
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        try:
+            p = json.load(open(path))
+            return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"]), "source": "measured"}
+        except (KeyError, ValueError, TypeError):
+            pass
+    return dict(FALLBACK_PEAKS)
+
+
+class ClockSampler:
+    """nvidia-smi in the background while a region is timed (reads only; nothing is set)."""
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_id: str):
+        self.gpu_id, self.proc, self.lines = gpu_id, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", self.gpu_id, f"--query-gpu={self.QUERY}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        self.lines += [l for l in out.splitlines() if l.strip()]
+        self.proc = None
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for l in self.lines:
+            f = [x.strip() for x in l.split(",")]
+            try:
+                sm.append(float(f[0])), mx.append(float(f[1]))
+            except (ValueError, IndexError):
+                continue
+            for name, v in zip(names, f[2:6]):
+                if v.lower() == "active":
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def decode_step_bytes(cfg, n_layers, batch, context_tokens):
+    """Bytes one decode step has to read: every weight it uses once (bfloat16), the embedding rows of the
+    batch, and the keys and values of the live requests."""
+    h, d = cfg["hidden_size"], cfg["head_dim"]
+    n_q, n_kv, inter, vocab = (cfg[k] for k in ("num_attention_heads", "num_key_value_heads", "intermediate_size",
+                                                "vocab_size"))
+    per_layer = ((n_q + 2 * n_kv) * d * h + h * n_q * d + 3 * inter * h + 2 * h + 2 * d) * 2
+    weights = n_layers * per_layer + (vocab * h + h) * 2 + batch * h * 2
+    kv = batch * context_tokens * n_layers * 2 * n_kv * d * 2
+    return weights + kv, weights, kv
+
+
+def prefill_flops(cfg, n_layers, tokens):
+    h, d = cfg["hidden_size"], cfg["head_dim"]
+    n_q, n_kv, inter, vocab = (cfg[k] for k in ("num_attention_heads", "num_key_value_heads", "intermediate_size",
+                                                "vocab_size"))
+    linear = 2 * tokens * ((n_q + 2 * n_kv) * d * h + h * n_q * d + 3 * inter * h)
+    attn = 4 * n_q * d * tokens * (tokens + 1) // 2
+    return n_layers * (linear + attn) + 2 * vocab * h
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration's 36 "
+                    "(layer sizes stay); the JSON names both numbers")
+    ap.add_argument("--no-points", action="store_true", help="skip decoding at batch 1 and 64")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "NikolayBlagoev/garlic-inference is a CMake C++/CUDA program built for sm_120a only, with "
+                          "no setup.py or pyproject.toml (pip: 'not installable'), and its runner cannot run the "
+                          "dense model"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported (nothing was run)")
+        return 2
+
+    import torch
+    from garlic_inference_b200 import LanguageModel, Qwen3Config
+    from garlic_inference_b200.ops import counters
+    from garlic_inference_b200.sampling import SamplingParams
+
+    K, W = args.steps, max(args.warmup, 3)
+    n_layers = args.layers or QWEN3_8B["num_hidden_layers"]
+    cfg = Qwen3Config(**{**QWEN3_8B, "num_hidden_layers": n_layers})
+    pk = peaks()
+    torch.cuda.set_device(0)
+    props = torch.cuda.get_device_properties(0)
+    gpu_id = "GPU-" + str(props.uuid) if getattr(props, "uuid", None) else "0"
+    batches = [args.batch] + ([] if args.no_points else [1, 64])
+    per_seq = -(-(CACHED + W + K + 8) // 64) * 64
+    max_tokens = max(max(batches) * per_seq, -(-PREFILL_TOKENS // 64) * 64 * 2)
+    model = LanguageModel.from_random(cfg, seed=0, device=0, dtype="bfloat16", max_tokens=max_tokens)
+    eng, sampler = model.engine, model.sampler
+    gen = torch.Generator().manual_seed(0)
+    greedy = SamplingParams()
+
+    def random_prompt(n):
+        return torch.randint(0, cfg.vocab_size, (n,), generator=gen).tolist()
+
+    def fill(batch):
+        """`batch` slots, each holding CACHED tokens after a real prefill; returns slots and next tokens."""
+        slots, firsts = [], []
+        for _ in range(batch):
+            s = eng.alloc_slot()
+            logits = model.step([(s, random_prompt(CACHED), [CACHED - 1])])
+            firsts.append(sampler.sample(logits, greedy, [0], [0]))
+            slots.append(s)
+        return slots, torch.cat(firsts)
+
+    def time_decode(batch, clocks=None):
+        slots, toks = fill(batch)
+        for _ in range(W):
+            toks = sampler.sample(eng.step_decode_device(slots, toks), greedy, slots, slots)
+        torch.cuda.synchronize()
+        launches0 = counters.launches
+        if clocks:
+            clocks.start()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(K):
+            toks = sampler.sample(eng.step_decode_device(slots, toks), greedy, slots, slots)
+        end.record()
+        torch.cuda.synchronize()
+        if clocks:
+            clocks.stop()
+        ms = start.elapsed_time(end)
+        launched = counters.launches - launches0
+        for s in slots:
+            eng.free_slot(s)
+        return batch * K / (ms / 1e3), ms / K, launched
+
+    # ---- prefill of 2,048 tokens --------------------------------------------------------------
+    prompt = random_prompt(PREFILL_TOKENS)
+    times = []
+    for i in range(3 + 3):
+        s = eng.alloc_slot()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        model.step([(s, prompt, [PREFILL_TOKENS - 1])])
+        b.record()
+        torch.cuda.synchronize()
+        eng.free_slot(s)
+        if i >= 3:
+            times.append(a.elapsed_time(b))
+    pre_ms = statistics.median(times)
+    pre_flops = prefill_flops(QWEN3_8B, n_layers, PREFILL_TOKENS)
+    prefill = {"value": PREFILL_TOKENS / (pre_ms / 1e3), "tokens": PREFILL_TOKENS, "ms": pre_ms,
+               "frac": pre_flops / (pre_ms / 1e3) / (pk["bf16_tflops"] * 1e12)}
+
+    # ---- decoding, timed on the device ----------------------------------------------------------
+    clocks = ClockSampler(gpu_id)
+    value, ms_per_step, launched = time_decode(args.batch, clocks)
+    avg_ctx = CACHED + W + (K + 1) / 2
+    total_b, weight_b, kv_b = decode_step_bytes(QWEN3_8B, n_layers, args.batch, avg_ctx)
+    achieved = total_b / (ms_per_step / 1e3) / 1e9
+    points = {}
+    if not args.no_points:
+        for b in (1, 64):
+            points[f"decode_b{b}"] = time_decode(b)[0]
+
+    # ---- the same through the entry point: host ids in, host ids out, every step ------------------
+    prompts = [random_prompt(CACHED) for _ in range(args.batch)]
+    model.generate(prompts[:1], max_new_tokens=4)                           # warm the path
+    up0 = eng._staging.bytes_uploaded
+    clocks.start()
+    out = model.generate(prompts, max_new_tokens=K + 1)
+    clocks.stop()
+    st = model.last_stats
+    e2e_steps = st.steps - 1
+    e2e = {"value": args.batch * e2e_steps / st.decode_seconds, "unit": "tokens/s",
+           "h2d_bytes_per_step": (eng._staging.bytes_uploaded - up0) / st.steps,
+           "d2h_bytes_per_step": 4 * args.batch}
+    assert all(len(o) == K + 1 for o in out)
+
+    line = {
+        "metric": f"decode tok/s at batch {args.batch} (Qwen3-8B layer sizes, {CACHED} cached tokens per sequence)",
+        "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": ms_per_step,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: random weights N(0, 0.02) made on the GPU, uniform random token ids",
+        "config": {"model": "Qwen3-8B layer sizes", "global_batch": args.batch, "seq_len": CONTEXT,
+                   "cached_tokens": CACHED, "parallelism": "none (1 GPU)", "layers_run": n_layers,
+                   "layers_config": QWEN3_8B["num_hidden_layers"], "hidden_size": 4096, "n_heads": 32,
+                   "n_kv_heads": 8, "head_dim": 128, "intermediate_size": 12288, "vocab_size": 151936,
+                   "page_size": eng.cache.page_size, "sampling": "greedy on the device",
+                   "l2": "inputs exceed L2: a step reads %.1f GB of weights" % (weight_b / 1e9)},
+        "clocks": clocks.summary(),
+        "e2e": e2e,
+        "gpu_launches": launched,
+        "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": achieved / pk["hbm_gbs"], "bytes_per_step": total_b, "peaks": pk["source"]},
+        "points": points,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,38 @@
+// Error channel shared by all entry points (see common.cuh).
+#include "common.cuh"
+
+#include <stdarg.h>
+#include <stdio.h>
+
+static thread_local char g_error[512] = "";
+
+void gi_set_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof(g_error), fmt, ap);
+    va_end(ap);
+}
+
+int gi_check_launch(const char* what) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        gi_set_error("%s: %s", what, cudaGetErrorString(e));
+        return (int)e;
+    }
+    return 0;
+}
+
+extern "C" const char* gi_last_error(void) { return g_error; }
+
+// Compute capability of the current device as major*10+minor, or a negative CUDA error.
+extern "C" int gi_device_arch(void) {
+    int dev = 0, major = 0, minor = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&minor, cudaDevAttrComputeCapabilityMinor, dev);
+    if (e != cudaSuccess) {
+        gi_set_error("gi_device_arch: %s", cudaGetErrorString(e));
+        return -(int)e;
+    }
+    return major * 10 + minor;
+}

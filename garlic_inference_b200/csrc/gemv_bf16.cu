@@ -1,0 +1,97 @@
+// bfloat16 matrix product for a handful of rows (decoding at small batch):
+// out[M,N] = x[M,K] . W[N,K]^T with M <= 8.  The step reads every weight once,
+// so the kernel is written for memory bandwidth: one warp per weight row, 16-byte
+// loads that bypass L1 for the weights, four loads in flight per lane, float32
+// accumulation, x read through L1 (all warps of an SM share it).
+//
+// Upstream calls a library product whatever M is (src/src-cuda/mat-ops/gemm/gemm.cu:22-41).
+#include "common.cuh"
+
+#define GV_WARPS 8
+
+__device__ __forceinline__ uint4 ld_stream(const uint4* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
+template <int M>
+__device__ __forceinline__ void fma8(const uint4& w, const bf16* __restrict__ x, int K, int k, float (&acc)[M]) {
+    const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&w);
+    float2 wf[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) wf[i] = __bfloat1622float2(w2[i]);
+#pragma unroll
+    for (int m = 0; m < M; ++m) {
+        const uint4 xv = __ldg(reinterpret_cast<const uint4*>(x + (size_t)m * K + k));
+        const __nv_bfloat162* x2 = reinterpret_cast<const __nv_bfloat162*>(&xv);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 xf = __bfloat1622float2(x2[i]);
+            acc[m] = fmaf(wf[i].x, xf.x, acc[m]);
+            acc[m] = fmaf(wf[i].y, xf.y, acc[m]);
+        }
+    }
+}
+
+template <int M, typename OutT>
+__global__ void __launch_bounds__(GV_WARPS * 32)
+gemv_bf16_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, OutT* __restrict__ out, int N, int K) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n = blockIdx.x * GV_WARPS + warp;
+    if (n >= N) return;
+    const uint4* wrow = reinterpret_cast<const uint4*>(W + (size_t)n * K);
+    const int nvec = K / 8;
+    float acc[M];
+#pragma unroll
+    for (int m = 0; m < M; ++m) acc[m] = 0.f;
+    int v = lane;
+    for (; v + 96 < nvec; v += 128) {
+        const uint4 w0 = ld_stream(wrow + v), w1 = ld_stream(wrow + v + 32);
+        const uint4 w2 = ld_stream(wrow + v + 64), w3 = ld_stream(wrow + v + 96);
+        fma8<M>(w0, x, K, v * 8, acc);
+        fma8<M>(w1, x, K, (v + 32) * 8, acc);
+        fma8<M>(w2, x, K, (v + 64) * 8, acc);
+        fma8<M>(w3, x, K, (v + 96) * 8, acc);
+    }
+    for (; v < nvec; v += 32) {
+        const uint4 w0 = ld_stream(wrow + v);
+        fma8<M>(w0, x, K, v * 8, acc);
+    }
+#pragma unroll
+    for (int m = 0; m < M; ++m) {
+        const float s = warp_sum(acc[m]);
+        if (lane == 0) out[(size_t)m * N + n] = from_f32<OutT>(s);
+    }
+}
+
+template <typename OutT>
+static int launch_gemv(const bf16* x, const bf16* W, OutT* out, int M, int N, int K, cudaStream_t s) {
+    const int blocks = (N + GV_WARPS - 1) / GV_WARPS;
+    switch (M) {
+        case 1: gemv_bf16_kernel<1, OutT><<<blocks, GV_WARPS * 32, 0, s>>>(x, W, out, N, K); break;
+        case 2: gemv_bf16_kernel<2, OutT><<<blocks, GV_WARPS * 32, 0, s>>>(x, W, out, N, K); break;
+        case 3: gemv_bf16_kernel<3, OutT><<<blocks, GV_WARPS * 32, 0, s>>>(x, W, out, N, K); break;
+        case 4: gemv_bf16_kernel<4, OutT><<<blocks, GV_WARPS * 32, 0, s>>>(x, W, out, N, K); break;
+        case 5: gemv_bf16_kernel<5, OutT><<<blocks, GV_WARPS * 32, 0, s>>>(x, W, out, N, K); break;
+        case 6: gemv_bf16_kernel<6, OutT><<<blocks, GV_WARPS * 32, 0, s>>>(x, W, out, N, K); break;
+        case 7: gemv_bf16_kernel<7, OutT><<<blocks, GV_WARPS * 32, 0, s>>>(x, W, out, N, K); break;
+        case 8: gemv_bf16_kernel<8, OutT><<<blocks, GV_WARPS * 32, 0, s>>>(x, W, out, N, K); break;
+        default: GI_REQUIRE(false, "gi_gemv_bf16: %d rows; this kernel takes 1 to 8", M);
+    }
+    return gi_check_launch("gi_gemv_bf16");
+}
+
+// out_dtype: GI_DTYPE_BF16 or GI_DTYPE_F32.  x, W and out are dense row-major.
+extern "C" int gi_gemv_bf16(const void* x, const void* W, void* out, int out_dtype, int M, int N, int K,
+                            void* stream) {
+    GI_REQUIRE(M >= 1 && M <= 8, "gi_gemv_bf16: %d rows; this kernel takes 1 to 8", M);
+    GI_REQUIRE(N > 0 && K > 0, "gi_gemv_bf16: sizes must be positive");
+    GI_REQUIRE(K % 8 == 0, "gi_gemv_bf16: inner size %d is no multiple of 8 (rows must start on 16 bytes)", K);
+    GI_REQUIRE(((uintptr_t)x % 16 == 0) && ((uintptr_t)W % 16 == 0), "gi_gemv_bf16: operands must start on 16 bytes");
+    cudaStream_t s = (cudaStream_t)stream;
+    if (out_dtype == GI_DTYPE_BF16) return launch_gemv<bf16>((const bf16*)x, (const bf16*)W, (bf16*)out, M, N, K, s);
+    if (out_dtype == GI_DTYPE_F32) return launch_gemv<float>((const bf16*)x, (const bf16*)W, (float*)out, M, N, K, s);
+    GI_REQUIRE(false, "gi_gemv_bf16: output dtype %d", out_dtype);
+}

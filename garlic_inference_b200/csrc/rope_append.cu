@@ -1,0 +1,127 @@
+// Per-head RMSNorm of q and k, rotary position encoding, and the write of the
+// new keys and values into the paged cache, in one pass over the projection
+// output.
+//
+// Upstream does this as two RMSNorm launches over head_dim, two rotation
+// launches, three transposes, a cache-append kernel and a length-increment
+// kernel (src/models/qwen3/qwen3.cpp:149-168, src/src-cuda/rope.cu:109-131,
+// src/src-cuda/kvcache.cu:7-45).  The arithmetic is theirs: the norm over
+// the whole head with the weight as it is, then rotate-half
+//   y[i]        = x[i] cos - x[i+r/2] sin
+//   y[i + r/2]  = x[i+r/2] cos + x[i] sin        for i < r/2,  r = rotary_dim
+// with dimensions beyond r passed through.  All of it is float32, rounded once.
+//
+// Layouts: qkv [n_tokens, (n_q + 2 n_kv) * d] (q heads, then k heads, then v
+// heads); q_out [n_tokens, n_q, d]; cache pools [n_pages, n_kv, page_size, d];
+// block_table [n_slots, max_pages] maps a slot's logical page to a pool page;
+// cos/sin [max_positions, r/2] float32.  A token whose slot is negative is
+// padding: its q is still written, nothing goes to the cache.
+#include "common.cuh"
+
+#define ROPE_WARPS 4
+
+template <typename T>
+__global__ void qk_norm_rope_append_kernel(
+    const T* __restrict__ qkv, T* __restrict__ q_out, T* __restrict__ k_pool, T* __restrict__ v_pool,
+    const void* __restrict__ q_w, const void* __restrict__ k_w, int w_dtype, float eps,
+    const float* __restrict__ cos_t, const float* __restrict__ sin_t, int rotary_dim,
+    const int* __restrict__ tok_pos, const int* __restrict__ tok_slot, const int* __restrict__ block_table,
+    int n_tokens, int n_q, int n_kv, int d, int page_size, int max_pages, int n_pool_pages,
+    int max_positions, int append, int* __restrict__ status) {
+    extern __shared__ float head_buf[];            // ROPE_WARPS * d floats
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int heads_here = append ? n_q + 2 * n_kv : n_q;
+    const long long item = (long long)blockIdx.x * ROPE_WARPS + warp;
+    if (item >= (long long)n_tokens * heads_here) return;
+    const int t = (int)(item / heads_here);
+    const int h = (int)(item - (long long)t * heads_here);
+    const int row_w = (n_q + 2 * n_kv) * d;
+    const T* src = qkv + (size_t)t * row_w + (size_t)h * d;
+    float* buf = head_buf + warp * d;
+
+    const bool is_q = h < n_q;
+    const bool is_k = !is_q && h < n_q + n_kv;
+    const int kvh = is_q ? 0 : (is_k ? h - n_q : h - n_q - n_kv);
+
+    // destination
+    T* dst;
+    const int pos = tok_pos[t];
+    if (is_q) {
+        dst = q_out + ((size_t)t * n_q + h) * d;
+    } else {
+        const int slot = tok_slot[t];
+        if (slot < 0) return;
+        const int lp = pos / page_size;
+        if (pos < 0 || lp >= max_pages) { if (lane == 0) atomicExch(status, 1); return; }
+        const int page = block_table[(size_t)slot * max_pages + lp];
+        if (page < 0 || page >= n_pool_pages) { if (lane == 0) atomicExch(status, 2); return; }
+        T* pool = is_k ? k_pool : v_pool;
+        dst = pool + (((size_t)page * n_kv + kvh) * page_size + (pos - lp * page_size)) * d;
+    }
+
+    if (!is_q && !is_k) {                          // values: copy
+        for (int i = lane; i < d; i += 32) dst[i] = src[i];
+        return;
+    }
+
+    float ss = 0.f;
+    for (int i = lane; i < d; i += 32) {
+        const float x = to_f32(src[i]);
+        buf[i] = x;
+        ss += x * x;
+    }
+    const void* w = is_q ? q_w : k_w;
+    float inv = 1.f;
+    if (w) inv = rsqrtf(warp_sum(ss) / (float)d + eps);
+    __syncwarp();
+    if (pos < 0 || pos >= max_positions) { if (lane == 0) atomicExch(status, 3); return; }
+    const int half = rotary_dim / 2;
+    const float* cs = cos_t + (size_t)pos * half;
+    const float* sn = sin_t + (size_t)pos * half;
+    for (int i = lane; i < d; i += 32) {
+        float y;
+        if (i < rotary_dim) {
+            const int j = i < half ? i : i - half;
+            const float a = w ? buf[j] * inv * load_w(w, w_dtype, j) : buf[j];
+            const float b = w ? buf[j + half] * inv * load_w(w, w_dtype, j + half) : buf[j + half];
+            // upstream rounds the normed value to the activation type before it rotates;
+            // here it stays float32 until the single rounding at the end
+            y = i < half ? a * cs[j] - b * sn[j] : b * cs[j] + a * sn[j];
+        } else {
+            y = w ? buf[i] * inv * load_w(w, w_dtype, i) : buf[i];
+        }
+        dst[i] = from_f32<T>(y);
+    }
+}
+
+extern "C" int gi_qk_norm_rope_append(
+    const void* qkv, void* q_out, void* k_pool, void* v_pool, int act_dtype,
+    const void* q_w, const void* k_w, int w_dtype, float eps,
+    const float* cos_t, const float* sin_t, int rotary_dim,
+    const int* tok_pos, const int* tok_slot, const int* block_table,
+    int n_tokens, int n_q, int n_kv, int d, int page_size, int max_pages, int n_pool_pages,
+    int max_positions, int append, int* status, void* stream) {
+    GI_REQUIRE(n_tokens >= 0 && n_q > 0 && n_kv > 0 && d > 0, "gi_qk_norm_rope_append: sizes must be positive");
+    GI_REQUIRE(rotary_dim >= 0 && rotary_dim <= d && rotary_dim % 2 == 0,
+               "gi_qk_norm_rope_append: rotary_dim %d must be even and at most head_dim %d", rotary_dim, d);
+    GI_REQUIRE(d <= 1024, "gi_qk_norm_rope_append: head_dim %d is beyond 1024", d);
+    GI_REQUIRE(page_size > 0 && max_pages > 0, "gi_qk_norm_rope_append: page sizes must be positive");
+    GI_REQUIRE((q_w == nullptr) == (k_w == nullptr), "gi_qk_norm_rope_append: q and k norm weights go together");
+    if (n_tokens == 0) return 0;
+    const int heads_here = append ? n_q + 2 * n_kv : n_q;
+    const long long items = (long long)n_tokens * heads_here;
+    const long long blocks = (items + ROPE_WARPS - 1) / ROPE_WARPS;
+    GI_REQUIRE(blocks < 2147483647LL, "gi_qk_norm_rope_append: too many (token, head) pairs");
+    const size_t smem = (size_t)ROPE_WARPS * d * sizeof(float);
+    cudaStream_t s = (cudaStream_t)stream;
+#define LAUNCH(T)                                                                                     \
+    qk_norm_rope_append_kernel<T><<<(int)blocks, ROPE_WARPS * 32, smem, s>>>(                         \
+        (const T*)qkv, (T*)q_out, (T*)k_pool, (T*)v_pool, q_w, k_w, w_dtype, eps, cos_t, sin_t,       \
+        rotary_dim, tok_pos, tok_slot, block_table, n_tokens, n_q, n_kv, d, page_size, max_pages,     \
+        n_pool_pages, max_positions, append, status)
+    if (act_dtype == GI_DTYPE_F32) LAUNCH(float);
+    else if (act_dtype == GI_DTYPE_BF16) LAUNCH(bf16);
+    else GI_REQUIRE(false, "gi_qk_norm_rope_append: activation dtype %d", act_dtype);
+#undef LAUNCH
+    return gi_check_launch("gi_qk_norm_rope_append");
+}

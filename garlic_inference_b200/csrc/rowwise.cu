@@ -1,0 +1,204 @@
+// Row-wise kernels: token embedding, residual add + RMSNorm, SwiGLU, casts.
+//
+// The residual stream is float32 in both precisions of the engine; T is the
+// activation type (float or bfloat16).  Norms and the residual sum are
+// computed in float32 and rounded once.
+//
+// Upstream counterparts: embedding rows (src/src-cuda/embedding.cu:29-53),
+// RMSNorm and add+RMSNorm (src/src-cuda/norm.cu:3-101), SiLU then a product
+// as two kernels (src/src-cuda/activations/silu.cu:35-67,
+// src/src-cuda/mat-ops/simple-ops/hadamard.cu:48-67).
+#include "common.cuh"
+
+// ---------------------------------------------------------------- embedding
+// out[t, :] = table[ids[t], :] as float32.  An id outside [0, vocab) writes zeros.
+template <typename T>
+__global__ void embedding_kernel(const int* __restrict__ ids, const T* __restrict__ table,
+                                 float* __restrict__ out, int vocab, int hidden) {
+    const int t = blockIdx.x;
+    const int id = ids[t];
+    float* dst = out + (size_t)t * hidden;
+    if (id < 0 || id >= vocab) {
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = 0.f;
+        return;
+    }
+    const T* src = table + (size_t)id * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = to_f32(src[i]);
+}
+
+extern "C" int gi_embedding(const int* ids, const void* table, int table_dtype, float* out,
+                            int n_tokens, int vocab, int hidden, void* stream) {
+    GI_REQUIRE(n_tokens >= 0 && vocab > 0 && hidden > 0, "gi_embedding: sizes must be positive");
+    if (n_tokens == 0) return 0;
+    const int threads = hidden >= 1024 ? 256 : 128;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (table_dtype == GI_DTYPE_F32)
+        embedding_kernel<float><<<n_tokens, threads, 0, s>>>(ids, (const float*)table, out, vocab, hidden);
+    else if (table_dtype == GI_DTYPE_BF16)
+        embedding_kernel<bf16><<<n_tokens, threads, 0, s>>>(ids, (const bf16*)table, out, vocab, hidden);
+    else
+        GI_REQUIRE(false, "gi_embedding: table dtype %d is neither float32 nor bfloat16", table_dtype);
+    return gi_check_launch("gi_embedding");
+}
+
+// ------------------------------------------------------- residual add + RMSNorm
+// For output row r (input row i = rows ? rows[r] : r):
+//   s = residual[i] (+ delta[i] when delta is given)        float32
+//   if write_residual: residual[i] = s
+//   out[r] = s * rsqrt(mean(s^2) + eps) * weight            rounded once to T
+// The block size depends on `dim` alone, so a row's result does not depend on
+// how many rows are in the launch.
+template <typename T>
+__global__ void add_rmsnorm_kernel(const T* __restrict__ delta, float* __restrict__ residual,
+                                   const void* __restrict__ weight, int w_dtype, T* __restrict__ out,
+                                   const int* __restrict__ rows, int dim, float eps, int write_residual) {
+    __shared__ float red[33];
+    const int r = blockIdx.x;
+    const size_t i = rows ? (size_t)rows[r] : (size_t)r;
+    float* res = residual + i * dim;
+    const T* del = delta ? delta + i * dim : nullptr;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < dim; c += blockDim.x) {
+        float s = res[c];
+        if (del) s += to_f32(del[c]);
+        if (write_residual && del) res[c] = s;
+        ss += s * s;
+    }
+    ss = block_sum(ss, red);
+    const float inv = rsqrtf(ss / (float)dim + eps);
+    T* o = out + (size_t)r * dim;
+    for (int c = threadIdx.x; c < dim; c += blockDim.x) {
+        float s = res[c];
+        if (del && !write_residual) s += to_f32(del[c]);
+        o[c] = from_f32<T>(s * inv * load_w(weight, w_dtype, c));
+    }
+}
+
+extern "C" int gi_add_rmsnorm(const void* delta, float* residual, const void* weight, int w_dtype,
+                              void* out, int act_dtype, const int* rows, int n_rows, int dim,
+                              float eps, int write_residual, void* stream) {
+    GI_REQUIRE(n_rows >= 0 && dim > 0, "gi_add_rmsnorm: sizes must be positive");
+    GI_REQUIRE(w_dtype == GI_DTYPE_F32 || w_dtype == GI_DTYPE_BF16, "gi_add_rmsnorm: weight dtype %d", w_dtype);
+    GI_REQUIRE(!(rows && write_residual), "gi_add_rmsnorm: gathered rows cannot write the residual back");
+    if (n_rows == 0) return 0;
+    const int threads = dim >= 2048 ? 512 : (dim >= 512 ? 256 : (dim >= 128 ? 128 : 32));
+    cudaStream_t s = (cudaStream_t)stream;
+    if (act_dtype == GI_DTYPE_F32)
+        add_rmsnorm_kernel<float><<<n_rows, threads, 0, s>>>((const float*)delta, residual, weight, w_dtype,
+                                                             (float*)out, rows, dim, eps, write_residual);
+    else if (act_dtype == GI_DTYPE_BF16)
+        add_rmsnorm_kernel<bf16><<<n_rows, threads, 0, s>>>((const bf16*)delta, residual, weight, w_dtype,
+                                                            (bf16*)out, rows, dim, eps, write_residual);
+    else
+        GI_REQUIRE(false, "gi_add_rmsnorm: activation dtype %d", act_dtype);
+    return gi_check_launch("gi_add_rmsnorm");
+}
+
+// residual[i] += delta[i] (float32 sum), for arrangements that need the stream itself.
+template <typename T>
+__global__ void residual_add_kernel(const T* __restrict__ delta, float* __restrict__ residual, size_t n) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; i < n; i += stride) residual[i] += to_f32(delta[i]);
+}
+
+extern "C" int gi_residual_add(const void* delta, int act_dtype, float* residual, long long n, void* stream) {
+    GI_REQUIRE(n >= 0, "gi_residual_add: negative size");
+    if (n == 0) return 0;
+    const int threads = 256;
+    const int blocks = (int)((n + threads - 1) / threads < 4096 ? (n + threads - 1) / threads : 4096);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (act_dtype == GI_DTYPE_F32)
+        residual_add_kernel<float><<<blocks, threads, 0, s>>>((const float*)delta, residual, (size_t)n);
+    else if (act_dtype == GI_DTYPE_BF16)
+        residual_add_kernel<bf16><<<blocks, threads, 0, s>>>((const bf16*)delta, residual, (size_t)n);
+    else
+        GI_REQUIRE(false, "gi_residual_add: activation dtype %d", act_dtype);
+    return gi_check_launch("gi_residual_add");
+}
+
+// ------------------------------------------------------------------- SwiGLU
+// gate_up is [n, 2*inter]: the gate in the first `inter` columns, the up
+// projection in the last.  out[n, inter] = silu(gate) * up, in float32, rounded once.
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, size_t total) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; i < total; i += stride) {
+        const size_t row = i / inter;
+        const int c = (int)(i - row * inter);
+        const float g = to_f32(gate_up[row * 2 * inter + c]);
+        const float u = to_f32(gate_up[row * 2 * inter + inter + c]);
+        out[i] = from_f32<T>(g / (1.f + expf(-g)) * u);
+    }
+}
+
+// bfloat16, 8 columns a thread (inter must be a multiple of 8)
+__global__ void swiglu_bf16x8_kernel(const bf16* __restrict__ gate_up, bf16* __restrict__ out, int inter,
+                                     size_t total_vec) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    const int vec_per_row = inter / 8;
+    for (; i < total_vec; i += stride) {
+        const size_t row = i / vec_per_row;
+        const int c = (int)(i - row * vec_per_row) * 8;
+        const uint4 gv = *reinterpret_cast<const uint4*>(gate_up + row * 2 * inter + c);
+        const uint4 uv = *reinterpret_cast<const uint4*>(gate_up + row * 2 * inter + inter + c);
+        const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gv);
+        const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&uv);
+        uint4 ov;
+        __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&ov);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float2 g = __bfloat1622float2(g2[k]);
+            const float2 u = __bfloat1622float2(u2[k]);
+            o2[k] = __floats2bfloat162_rn(g.x / (1.f + expf(-g.x)) * u.x, g.y / (1.f + expf(-g.y)) * u.y);
+        }
+        *reinterpret_cast<uint4*>(out + row * inter + c) = ov;
+    }
+}
+
+extern "C" int gi_swiglu(const void* gate_up, void* out, int act_dtype, int n_rows, int inter, void* stream) {
+    GI_REQUIRE(n_rows >= 0 && inter > 0, "gi_swiglu: sizes must be positive");
+    if (n_rows == 0) return 0;
+    const size_t total = (size_t)n_rows * inter;
+    const int threads = 256;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (act_dtype == GI_DTYPE_BF16 && inter % 8 == 0) {
+        const size_t nv = total / 8;
+        const int blocks = (int)((nv + threads - 1) / threads < 65535 ? (nv + threads - 1) / threads : 65535);
+        swiglu_bf16x8_kernel<<<blocks, threads, 0, s>>>((const bf16*)gate_up, (bf16*)out, inter, nv);
+        return gi_check_launch("gi_swiglu");
+    }
+    const int blocks = (int)((total + threads - 1) / threads < 65535 ? (total + threads - 1) / threads : 65535);
+    if (act_dtype == GI_DTYPE_F32)
+        swiglu_kernel<float><<<blocks, threads, 0, s>>>((const float*)gate_up, (float*)out, inter, total);
+    else if (act_dtype == GI_DTYPE_BF16)
+        swiglu_kernel<bf16><<<blocks, threads, 0, s>>>((const bf16*)gate_up, (bf16*)out, inter, total);
+    else
+        GI_REQUIRE(false, "gi_swiglu: activation dtype %d", act_dtype);
+    return gi_check_launch("gi_swiglu");
+}
+
+// -------------------------------------------------------------------- casts
+template <typename S, typename D>
+__global__ void cast_kernel(const S* __restrict__ src, D* __restrict__ dst, size_t n) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; i < n; i += stride) dst[i] = from_f32<D>(to_f32(src[i]));
+}
+
+extern "C" int gi_cast(const void* src, int src_dtype, void* dst, int dst_dtype, long long n, void* stream) {
+    GI_REQUIRE(n >= 0, "gi_cast: negative size");
+    if (n == 0) return 0;
+    const int threads = 256;
+    const int blocks = (int)((n + threads - 1) / threads < 65535 ? (n + threads - 1) / threads : 65535);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (src_dtype == GI_DTYPE_F32 && dst_dtype == GI_DTYPE_BF16)
+        cast_kernel<float, bf16><<<blocks, threads, 0, s>>>((const float*)src, (bf16*)dst, (size_t)n);
+    else if (src_dtype == GI_DTYPE_BF16 && dst_dtype == GI_DTYPE_F32)
+        cast_kernel<bf16, float><<<blocks, threads, 0, s>>>((const bf16*)src, (float*)dst, (size_t)n);
+    else
+        GI_REQUIRE(false, "gi_cast: from dtype %d to dtype %d", src_dtype, dst_dtype);
+    return gi_check_launch("gi_cast");
+}

@@ -1,0 +1,233 @@
+"""Python faces of the CUDA entry points.
+
+Each function checks that its tensors are on the GPU, dense and of the types
+the kernel is written for, allocates the output, and launches on torch's
+current stream.  Sizes a kernel cannot take come back as `KernelError` with
+the kernel's own message.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .library import KernelError, check, require_gpu
+
+F32, BF16 = 0, 1
+_CODES = {torch.float32: F32, torch.bfloat16: BF16}
+
+
+def code(dtype: torch.dtype) -> int:
+    try:
+        return _CODES[dtype]
+    except KeyError:
+        raise KernelError(f"dtype {dtype} is neither float32 nor bfloat16") from None
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _dense(t: torch.Tensor, name: str, dtype=None) -> torch.Tensor:
+    if not t.is_cuda:
+        raise KernelError(f"{name} is on {t.device}; the kernels run on the GPU only")
+    if not t.is_contiguous():
+        raise KernelError(f"{name} of shape {tuple(t.shape)} and strides {t.stride()} is not dense")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} is {t.dtype}, the kernel wants {dtype}")
+    return t
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def embedding(ids: torch.Tensor, table: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """float32 rows of `table` for int32 `ids`: the start of the residual stream."""
+    l = require_gpu()
+    _dense(ids, "ids", torch.int32)
+    _dense(table, "table")
+    n, (vocab, hidden) = ids.numel(), table.shape
+    if out is None:
+        out = torch.empty((n, hidden), dtype=torch.float32, device=table.device)
+    _dense(out, "out", torch.float32)
+    check(l.gi_embedding(_ptr(ids), _ptr(table), code(table.dtype), _ptr(out), n, vocab, hidden, _stream()), l)
+    return out
+
+
+def add_rmsnorm(delta: Optional[torch.Tensor], residual: torch.Tensor, weight: torch.Tensor, eps: float,
+                act_dtype: torch.dtype, rows: Optional[torch.Tensor] = None,
+                write_residual: bool = True, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """normed = rmsnorm(residual (+ delta)) * weight in `act_dtype`; with `write_residual` the
+    float32 sum goes back into `residual`.  `rows` (int32) picks input rows (then nothing is written back)."""
+    l = require_gpu()
+    _dense(residual, "residual", torch.float32)
+    _dense(weight, "weight")
+    dim = residual.shape[-1]
+    if weight.numel() != dim:
+        raise KernelError(f"norm weight has {weight.numel()} elements for rows of {dim}")
+    if delta is not None:
+        _dense(delta, "delta", act_dtype)
+        if delta.shape != residual.shape:
+            raise KernelError(f"delta {tuple(delta.shape)} and residual {tuple(residual.shape)} differ")
+    if rows is not None:
+        _dense(rows, "rows", torch.int32)
+        n_rows, write_residual = rows.numel(), False
+    else:
+        n_rows = residual.numel() // dim
+    if out is None:
+        out = torch.empty((n_rows, dim), dtype=act_dtype, device=residual.device)
+    _dense(out, "out", act_dtype)
+    check(l.gi_add_rmsnorm(_ptr(delta), _ptr(residual), _ptr(weight), code(weight.dtype), _ptr(out),
+                           code(act_dtype), _ptr(rows), n_rows, dim, float(eps), int(write_residual), _stream()), l)
+    return out
+
+
+def residual_add(delta: torch.Tensor, residual: torch.Tensor) -> None:
+    l = require_gpu()
+    _dense(delta, "delta")
+    _dense(residual, "residual", torch.float32)
+    if delta.shape != residual.shape:
+        raise KernelError(f"delta {tuple(delta.shape)} and residual {tuple(residual.shape)} differ")
+    check(l.gi_residual_add(_ptr(delta), code(delta.dtype), _ptr(residual), residual.numel(), _stream()), l)
+
+
+def swiglu(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """silu(gate) * up for [n, 2*inter] rows holding the gate first, then up."""
+    l = require_gpu()
+    _dense(gate_up, "gate_up")
+    n, two_i = gate_up.shape
+    if two_i % 2:
+        raise KernelError(f"gate_up rows of {two_i} columns cannot hold a gate and an up half")
+    if out is None:
+        out = torch.empty((n, two_i // 2), dtype=gate_up.dtype, device=gate_up.device)
+    _dense(out, "out", gate_up.dtype)
+    check(l.gi_swiglu(_ptr(gate_up), _ptr(out), code(gate_up.dtype), n, two_i // 2, _stream()), l)
+    return out
+
+
+def cast(src: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    if src.dtype == dtype:
+        return src
+    l = require_gpu()
+    _dense(src, "src")
+    out = torch.empty(src.shape, dtype=dtype, device=src.device)
+    check(l.gi_cast(_ptr(src), code(src.dtype), _ptr(out), code(dtype), src.numel(), _stream()), l)
+    return out
+
+
+def qk_norm_rope_append(qkv: torch.Tensor, n_q: int, n_kv: int, head_dim: int,
+                        q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,
+                        cos: torch.Tensor, sin: torch.Tensor, rotary_dim: int,
+                        tok_pos: torch.Tensor, tok_slot: torch.Tensor,
+                        k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: torch.Tensor,
+                        status: torch.Tensor, append: bool = True) -> torch.Tensor:
+    """Norm and rotate q and k of packed projections [n, (n_q + 2 n_kv) d]; returns q [n, n_q, d]
+    and (with `append`) writes k and v of every token with a slot into the paged pools."""
+    l = require_gpu()
+    act = qkv.dtype
+    _dense(qkv, "qkv")
+    n = qkv.shape[0]
+    if qkv.shape[1] != (n_q + 2 * n_kv) * head_dim:
+        raise KernelError(f"qkv rows have {qkv.shape[1]} columns, not (n_q + 2 n_kv) * head_dim = "
+                          f"{(n_q + 2 * n_kv) * head_dim}")
+    for t, name in ((k_pool, "k_pool"), (v_pool, "v_pool")):
+        _dense(t, name, act)
+    n_pages, pool_kv, page_size, pool_d = k_pool.shape
+    if (pool_kv, pool_d) != (n_kv, head_dim) or v_pool.shape != k_pool.shape:
+        raise KernelError(f"cache pools {tuple(k_pool.shape)} / {tuple(v_pool.shape)} do not fit "
+                          f"{n_kv} key/value heads of {head_dim}")
+    _dense(cos, "cos", torch.float32), _dense(sin, "sin", torch.float32)
+    if cos.shape != sin.shape or cos.shape[1] * 2 != rotary_dim:
+        raise KernelError(f"rotary tables {tuple(cos.shape)} do not fit rotary_dim {rotary_dim}")
+    for t, name in ((tok_pos, "tok_pos"), (tok_slot, "tok_slot"), (block_table, "block_table"), (status, "status")):
+        _dense(t, name, torch.int32)
+    if tok_pos.numel() < n or tok_slot.numel() < n:
+        raise KernelError("tok_pos / tok_slot are shorter than the token rows")
+    w_code = F32
+    if q_weight is not None:
+        _dense(q_weight, "q_weight"), _dense(k_weight, "k_weight", q_weight.dtype)
+        if q_weight.numel() != head_dim or k_weight.numel() != head_dim:
+            raise KernelError("q/k norm weights must have head_dim elements")
+        w_code = code(q_weight.dtype)
+    q_out = torch.empty((n, n_q, head_dim), dtype=act, device=qkv.device)
+    check(l.gi_qk_norm_rope_append(
+        _ptr(qkv), _ptr(q_out), _ptr(k_pool), _ptr(v_pool), code(act), _ptr(q_weight), _ptr(k_weight), w_code,
+        float(eps), _ptr(cos), _ptr(sin), rotary_dim, _ptr(tok_pos), _ptr(tok_slot), _ptr(block_table),
+        n, n_q, n_kv, head_dim, page_size, block_table.shape[1], n_pages, cos.shape[0], int(append),
+        _ptr(status), _stream()), l)
+    return q_out
+
+
+def attention_generic(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: torch.Tensor,
+                      tok_pos: torch.Tensor, tok_slot: torch.Tensor, scale: float, window: int,
+                      status: torch.Tensor) -> torch.Tensor:
+    """Exact-order attention of q [n, n_q, d] over the paged cache; returns [n, n_q * d]."""
+    l = require_gpu()
+    _dense(q, "q")
+    n, n_q, d = q.shape
+    _dense(k_pool, "k_pool", q.dtype), _dense(v_pool, "v_pool", q.dtype)
+    n_pages, n_kv, page_size, pool_d = k_pool.shape
+    if pool_d != d or v_pool.shape != k_pool.shape:
+        raise KernelError(f"cache pools {tuple(k_pool.shape)} do not fit head_dim {d}")
+    for t, name in ((tok_pos, "tok_pos"), (tok_slot, "tok_slot"), (block_table, "block_table"), (status, "status")):
+        _dense(t, name, torch.int32)
+    out = torch.empty((n, n_q * d), dtype=q.dtype, device=q.device)
+    check(l.gi_attention_generic(_ptr(q), _ptr(k_pool), _ptr(v_pool), code(q.dtype), _ptr(block_table),
+                                 _ptr(tok_pos), _ptr(tok_slot), _ptr(out), n, n_q, n_kv, d, page_size,
+                                 block_table.shape[1], n_pages, int(window or 0), float(scale), _ptr(status),
+                                 _stream()), l)
+    return out
+
+
+def sgemm_nt(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """a [M,K] . w[N,K]^T in true float32."""
+    l = require_gpu()
+    _dense(a, "a", torch.float32), _dense(w, "w", torch.float32)
+    (m, k), (n, k2) = a.shape, w.shape
+    if k != k2:
+        raise KernelError(f"inner sizes differ: a {tuple(a.shape)}, w {tuple(w.shape)}")
+    if out is None:
+        out = torch.empty((m, n), dtype=torch.float32, device=a.device)
+    _dense(out, "out", torch.float32)
+    check(l.gi_sgemm_nt(_ptr(a), _ptr(w), _ptr(out), m, n, k, k, n, _stream()), l)
+    return out
+
+
+def gemv_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """x [M<=8, K] . w[N,K]^T, bfloat16 operands, float32 accumulation."""
+    l = require_gpu()
+    _dense(x, "x", torch.bfloat16), _dense(w, "w", torch.bfloat16)
+    (m, k), (n, k2) = x.shape, w.shape
+    if k != k2:
+        raise KernelError(f"inner sizes differ: x {tuple(x.shape)}, w {tuple(w.shape)}")
+    out = torch.empty((m, n), dtype=out_dtype, device=x.device)
+    check(l.gi_gemv_bf16(_ptr(x), _ptr(w), _ptr(out), code(out_dtype), m, n, k, _stream()), l)
+    return out
+
+
+def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor], streams: Optional[torch.Tensor],
+           counters: Optional[torch.Tensor], seed: int, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One token per row of float32 logits [n, vocab]: greedy where temperature <= 0 (or None),
+    else a draw from softmax(logits / temperature) keyed by (seed, streams[row], counters[row])."""
+    l = require_gpu()
+    if logits.dim() != 2 or logits.stride(1) != 1:
+        raise KernelError("logits must be [rows, vocab] with dense rows")
+    if not logits.is_cuda or logits.dtype != torch.float32:
+        raise KernelError("logits must be float32 on the GPU")
+    n, vocab = logits.shape
+    if temperature is not None:
+        _dense(temperature, "temperature", torch.float32)
+    if streams is not None:
+        _dense(streams, "streams", torch.int64)
+    if counters is not None:
+        _dense(counters, "counters", torch.int32)
+    for t, name in ((temperature, "temperature"), (streams, "streams"), (counters, "counters")):
+        if t is not None and t.numel() < n:
+            raise KernelError(f"{name} has fewer entries than logits has rows")
+    if out is None:
+        out = torch.empty((n,), dtype=torch.int32, device=logits.device)
+    _dense(out, "out", torch.int32)
+    check(l.gi_sample(_ptr(logits), logits.stride(0), n, vocab, _ptr(temperature), _ptr(streams), _ptr(counters),
+                      int(seed) & 0xFFFFFFFFFFFFFFFF, _ptr(out), _stream()), l)
+    return out

@@ -1,0 +1,43 @@
+"""y = x W^T for a weight stored [out, in], the way every projection here is.
+
+Which product runs:
+  * float32 weight: this package's own float32 FMA kernel (no tensor-core or
+    reduced-precision mode); bfloat16 activations are widened first and the
+    result narrowed again.
+  * bfloat16 weight, up to 8 rows: this package's bandwidth kernel.
+  * bfloat16 weight, more rows: the library product (cuBLAS through
+    `torch.mm`), float32 accumulation.  Upstream uses the same library for all
+    its products (src/src-cuda/mat-ops/gemm/gemm.cu:22-41).
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import kernels
+from .library import KernelError
+
+GEMV_MAX_ROWS = 8
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    if x.dim() != 2 or w.dim() != 2 or x.shape[1] != w.shape[1]:
+        raise KernelError(f"linear: x {tuple(x.shape)} does not fit a weight {tuple(w.shape)} ([out, in])")
+    out_dtype = out_dtype or x.dtype
+    if w.dtype == torch.float32:
+        y = kernels.sgemm_nt(kernels.cast(x, torch.float32), w)
+        return kernels.cast(y, out_dtype)
+    if w.dtype != torch.bfloat16:
+        raise KernelError(f"linear: weight dtype {w.dtype}")
+    if x.dtype != torch.bfloat16:
+        raise KernelError(f"linear: a bfloat16 weight takes bfloat16 activations, not {x.dtype}")
+    m, k = x.shape
+    if m == 0:
+        return torch.empty((0, w.shape[0]), dtype=out_dtype, device=x.device)
+    if m <= GEMV_MAX_ROWS and k % 8 == 0 and w.data_ptr() % 16 == 0 and x.data_ptr() % 16 == 0:
+        return kernels.gemv_bf16(x, w, out_dtype)
+    kernels.require_gpu()
+    if out_dtype == torch.float32:
+        return torch.mm(x, w.t(), out_dtype=torch.float32)
+    return torch.mm(x, w.t())

@@ -1,0 +1,6 @@
+from .loader import Checkpoint, TensorWant, WeightError, device_dtype
+from .random_init import RandomSource, random_tensor, write_random_model
+from .safetensors_io import SafetensorsError, SafetensorsFile, write_safetensors
+
+__all__ = ["Checkpoint", "TensorWant", "WeightError", "device_dtype", "RandomSource", "random_tensor",
+           "write_random_model", "SafetensorsError", "SafetensorsFile", "write_safetensors"]

@@ -1,0 +1,131 @@
+"""The generation loop's decisions, with a scripted stepper in place of the GPU engine (CPU)."""
+import pytest
+
+from garlic_inference_b200.engine import (GenerationError, GenerationLoop, GenParams, finished, plan_batches,
+                                          tokens_held)
+
+
+class ScriptedStepper:
+    """Stands in for the engine: 'logits' are the lists of (slot, fed tokens); the picker turns them
+    into the next token by a rule of the test.  Records every call."""
+
+    def __init__(self, n_slots=4):
+        self.free = list(range(n_slots - 1, -1, -1))
+        self.live = {}
+        self.calls = []
+        self.freed = []
+
+    def alloc_slot(self):
+        s = self.free.pop()
+        self.live[s] = 0
+        return s
+
+    def free_slot(self, s):
+        assert s in self.live, "slot freed twice or never given out"
+        del self.live[s]
+        self.free.append(s)
+        self.freed.append(s)
+
+    def step(self, entries):
+        for e in entries:
+            assert e.slot in self.live
+            self.live[e.slot] += len(e.tokens)
+        self.calls.append([(e.slot, list(e.tokens), list(e.want)) for e in entries])
+        return [(e.slot, list(e.tokens)) for e in entries]
+
+
+def counting_picker(log):
+    """Next token = last fed token + 1; logs (request ids, token indices) it was keyed with."""
+    def pick(logits, request_ids, token_indices, params):
+        log.append((list(request_ids), list(token_indices)))
+        return [toks[-1] + 1 for _, toks in logits]
+    return pick
+
+
+def loop(stepper, picker, capacity=4096, max_positions=1000, max_batch=4):
+    return GenerationLoop(stepper, picker, capacity, max_positions, max_batch)
+
+
+def test_unequal_prompts_one_prefill_then_one_token_each():
+    st, log = ScriptedStepper(), []
+    out = loop(st, counting_picker(log)).run([[10, 11, 12], [50], [70, 71]], GenParams(max_new_tokens=3))
+    assert out == [[13, 14, 15], [51, 52, 53], [72, 73, 74]]
+    assert st.calls[0] == [(0, [10, 11, 12], [2]), (1, [50], [0]), (2, [70, 71], [1])]
+    assert st.calls[1] == [(0, [13], [0]), (1, [51], [0]), (2, [72], [0])]
+    assert len(st.calls) == 3                      # the last token of each request is never fed back
+    assert log == [([0, 1, 2], [0, 0, 0]), ([0, 1, 2], [1, 1, 1]), ([0, 1, 2], [2, 2, 2])]
+    assert not st.live and sorted(st.freed) == [0, 1, 2]
+
+
+def test_stop_token_ends_a_request_early_and_the_batch_shrinks():
+    st = ScriptedStepper()
+    lp = loop(st, counting_picker([]))
+    out = lp.run([[1], [20], [97]], GenParams(max_new_tokens=6, stop_token_ids=(22, 98)))
+    assert out == [[2, 3, 4, 5, 6, 7], [21, 22], [98]]          # the stop token is the last one returned
+    assert [len(c) for c in st.calls] == [3, 2, 1, 1, 1, 1]
+    assert st.freed == [2, 1, 0]                                # given back as each ends
+    assert lp.stats.batch_sizes == [3, 2, 1, 1, 1, 1] and lp.stats.new_tokens == 9
+    assert lp.stats.prompt_tokens == 3 and lp.stats.batches == 1
+
+
+def test_more_requests_than_the_batch_holds_run_as_batches_one_after_another():
+    st = ScriptedStepper(n_slots=2)
+    lp = loop(st, counting_picker([]), max_batch=2)
+    prompts = [[i * 10] for i in range(5)]
+    out = lp.run(prompts, GenParams(max_new_tokens=2))
+    assert out == [[i * 10 + 1, i * 10 + 2] for i in range(5)]
+    assert lp.stats.batches == 3
+    prefill_calls = [c for c in st.calls if c[0][2] == [0] and len(c[0][1]) == 1 and c[0][1][0] % 10 == 0]
+    assert [len(c) for c in prefill_calls] == [2, 2, 1]
+    assert set(s for c in st.calls for s, _, _ in c) == {0, 1}          # two slots, used again
+    assert not st.live
+
+
+def test_capacity_cuts_batches_and_refuses_what_never_fits():
+    assert tokens_held(100, 30, 4096) == 192 and tokens_held(1, 1, 4096) == 64
+    assert tokens_held(4000, 500, 4096) == 4096
+    assert plan_batches([100, 100, 100], 29, 256, 4096, 8) == [[0, 1], [2]]
+    assert plan_batches([10] * 5, 5, 4096, 4096, 2) == [[0, 1], [2, 3], [4]]
+    with pytest.raises(GenerationError, match="request 1 may hold 320"):
+        plan_batches([10, 300], 10, 256, 4096, 8)
+    with pytest.raises(GenerationError, match="empty prompt"):
+        plan_batches([3, 0], 10, 256, 4096, 8)
+    with pytest.raises(GenerationError, match="takes 64 positions"):
+        plan_batches([65], 1, 256, 64, 8)
+
+
+def test_finish_rules():
+    p = GenParams(max_new_tokens=4, stop_token_ids=[7])
+    assert finished(7, 1, 10, p, 100) and finished(3, 4, 10, p, 100) and not finished(3, 3, 10, p, 100)
+    assert finished(3, 2, 98, p, 100) and not finished(3, 1, 98, p, 100)     # positions run out
+    with pytest.raises(GenerationError):
+        GenParams(max_new_tokens=-1)
+    with pytest.raises(GenerationError):
+        GenParams(temperature=-0.5)
+
+
+def test_positions_limit_ends_generation():
+    st = ScriptedStepper()
+    out = loop(st, counting_picker([]), max_positions=6).run([[1, 2, 3, 4]], GenParams(max_new_tokens=50))
+    assert out == [[5, 6]] and st.live == {}
+    assert max(sum(len(t) for s, t, _ in c) for c in st.calls) <= 4
+
+
+def test_zero_new_tokens_and_no_prompts_touch_nothing():
+    st = ScriptedStepper()
+    assert loop(st, counting_picker([])).run([[1, 2]], GenParams(max_new_tokens=0)) == [[]]
+    assert loop(st, counting_picker([])).run([], GenParams()) == []
+    assert st.calls == []
+
+
+def test_slots_are_given_back_when_a_step_fails():
+    class Failing(ScriptedStepper):
+        def step(self, entries):
+            if len(self.calls) == 1:
+                raise RuntimeError("boom")
+            return super().step(entries)
+
+    st = Failing()
+    with pytest.raises(RuntimeError, match="boom"):
+        loop(st, counting_picker([])).run([[1], [2]], GenParams(max_new_tokens=5))
+    assert not st.live and len(st.free) == 4

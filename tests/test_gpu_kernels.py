@@ -1,0 +1,379 @@
+"""Each CUDA kernel alone against a plain float32 torch computation of the same operation, at sizes
+other than the models' (odd widths, groups of 1 / 5 / 6, head sizes 16 / 48 / 128 / 256, pages that
+are crossed, windows)."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+
+
+def K():
+    from garlic_inference_b200.ops import kernels
+    return kernels
+
+
+def ulp_tol(dtype):
+    # bfloat16: a result rounded once from float32 may differ by one step of 2^-8 relative
+    return dict(rtol=2 ** -7, atol=1e-3) if dtype == torch.bfloat16 else dict(rtol=1e-5, atol=1e-6)
+
+
+# ------------------------------------------------------------------ row-wise kernels
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embedding(dtype):
+    g = torch.Generator(device=DEV).manual_seed(0)
+    table = torch.randn(77, 100, generator=g, device=DEV).to(dtype)
+    ids = torch.tensor([0, 76, 5, 5, 80, -1, 33], dtype=torch.int32, device=DEV)
+    out = K().embedding(ids, table)
+    assert out.dtype == torch.float32 and out.shape == (7, 100)
+    ok = [0, 1, 2, 3, 6]
+    assert torch.equal(out[ok], table[ids[ok].long()].float())
+    assert float(out[4].abs().sum()) == 0 and float(out[5].abs().sum()) == 0      # ids outside the table
+
+
+@pytest.mark.parametrize("act", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("wdt", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("dim", [48, 100, 1000, 4096])
+def test_add_rmsnorm(act, wdt, dim):
+    g = torch.Generator(device=DEV).manual_seed(dim)
+    res = torch.randn(9, dim, generator=g, device=DEV) * 3
+    delta = torch.randn(9, dim, generator=g, device=DEV).to(act)
+    w = (1 + 0.3 * torch.randn(dim, generator=g, device=DEV)).to(wdt)
+    eps = 3e-5
+
+    def ref(s):
+        return s * torch.rsqrt((s * s).mean(-1, keepdim=True) + eps) * w.float()
+
+    r1 = res.clone()
+    out = K().add_rmsnorm(delta, r1, w, eps, act)
+    s = res + delta.float()
+    assert torch.equal(r1, s), "the float32 sum goes back into the residual"
+    torch.testing.assert_close(out.float(), ref(s).to(act).float(), **ulp_tol(act))
+    r2 = res.clone()
+    out = K().add_rmsnorm(None, r2, w, eps, act)
+    assert torch.equal(r2, res)
+    torch.testing.assert_close(out.float(), ref(res).to(act).float(), **ulp_tol(act))
+    rows = torch.tensor([8, 0, 3], dtype=torch.int32, device=DEV)
+    r3 = res.clone()
+    out = K().add_rmsnorm(delta, r3, w, eps, act, rows=rows)
+    assert torch.equal(r3, res), "gathered rows leave the residual alone"
+    torch.testing.assert_close(out.float(), ref(s)[rows.long()].to(act).float(), **ulp_tol(act))
+
+
+def test_add_rmsnorm_row_result_does_not_depend_on_the_batch():
+    g = torch.Generator(device=DEV).manual_seed(1)
+    res = torch.randn(33, 1536, generator=g, device=DEV)
+    w = torch.randn(1536, generator=g, device=DEV)
+    whole = K().add_rmsnorm(None, res.clone(), w, 1e-6, torch.float32)
+    one = K().add_rmsnorm(None, res[17:18].clone(), w, 1e-6, torch.float32)
+    assert torch.equal(whole[17:18], one)
+
+
+@pytest.mark.parametrize("dtype,inter", [(torch.float32, 13), (torch.bfloat16, 13), (torch.bfloat16, 112)])
+def test_swiglu(dtype, inter):
+    g = torch.Generator(device=DEV).manual_seed(2)
+    gu = (torch.randn(11, 2 * inter, generator=g, device=DEV) * 4).to(dtype)
+    out = K().swiglu(gu)
+    gate, up = gu[:, :inter].float(), gu[:, inter:].float()
+    ref = (gate / (1 + torch.exp(-gate)) * up).to(dtype)
+    torch.testing.assert_close(out.float(), ref.float(), **ulp_tol(dtype))
+
+
+def test_cast_and_residual_add():
+    g = torch.Generator(device=DEV).manual_seed(3)
+    x = torch.randn(1001, generator=g, device=DEV)
+    b = K().cast(x, torch.bfloat16)
+    assert torch.equal(b, x.to(torch.bfloat16)) and torch.equal(K().cast(b, torch.float32), b.float())
+    res = torch.randn(7, 143, generator=g, device=DEV)
+    want = res + b[:1001].float().view(7, 143)
+    K().residual_add(b.view(7, 143), res)
+    assert torch.equal(res, want)
+
+
+# ------------------------------------------------------------------ products
+@pytest.mark.parametrize("m,n,k", [(1, 130, 50), (70, 130, 50), (64, 64, 16), (129, 65, 257)])
+def test_sgemm_is_true_float32(m, n, k):
+    g = torch.Generator(device=DEV).manual_seed(4)
+    a = torch.randn(m, k, generator=g, device=DEV)
+    w = torch.randn(n, k, generator=g, device=DEV)
+    out = K().sgemm_nt(a, w)
+    ref = (a.double() @ w.double().T)
+    # float32 accumulation of k terms: far below what a tensor-core or tf32 mode would leave (1e-3)
+    assert float((out.double() - ref).abs().max()) < 1e-5 * math.sqrt(k) * float(ref.abs().max())
+
+
+def test_sgemm_row_result_does_not_depend_on_the_batch():
+    g = torch.Generator(device=DEV).manual_seed(5)
+    a = torch.randn(150, 333, generator=g, device=DEV)
+    w = torch.randn(200, 333, generator=g, device=DEV)
+    whole = K().sgemm_nt(a, w)
+    for i in (0, 63, 64, 149):
+        assert torch.equal(whole[i:i + 1], K().sgemm_nt(a[i:i + 1].contiguous(), w))
+    assert torch.equal(whole[10:90], K().sgemm_nt(a[10:90].contiguous(), w))
+
+
+@pytest.mark.parametrize("m", [1, 2, 3, 5, 8])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_gemv_bf16(m, out_dtype):
+    g = torch.Generator(device=DEV).manual_seed(6)
+    n, k = 1003, 264 + 1024
+    x = torch.randn(m, k, generator=g, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(n, k, generator=g, device=DEV) * 0.1).to(torch.bfloat16)
+    out = K().gemv_bf16(x, w, out_dtype)
+    ref = x.float() @ w.float().T
+    assert out.dtype == out_dtype
+    if out_dtype == torch.float32:
+        torch.testing.assert_close(out, ref, rtol=1e-4, atol=1e-4)
+    else:
+        torch.testing.assert_close(out.float(), ref.to(torch.bfloat16).float(), **ulp_tol(torch.bfloat16))
+
+
+def test_kernels_refuse_what_they_cannot_take():
+    from garlic_inference_b200.ops import KernelError
+    x = torch.zeros(9, 64, dtype=torch.bfloat16, device=DEV)
+    w = torch.zeros(32, 64, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(KernelError, match="1 to 8"):
+        K().gemv_bf16(x, w, torch.float32)
+    with pytest.raises(KernelError, match="multiple of 8"):
+        K().gemv_bf16(x[:2, :60].contiguous(), w[:, :60].contiguous(), torch.float32)
+    with pytest.raises(KernelError, match="not dense"):
+        K().swiglu(x[:, ::2])
+    with pytest.raises(KernelError, match="GPU only"):
+        K().swiglu(x.cpu())
+    q = torch.zeros(2, 4, 20, dtype=torch.float32, device=DEV)
+    pool = torch.zeros(4, 2, 16, 20, dtype=torch.float32, device=DEV)
+    bt = torch.zeros(1, 4, dtype=torch.int32, device=DEV)
+    z = torch.zeros(2, dtype=torch.int32, device=DEV)
+    with pytest.raises(KernelError, match="multiple of 8"):
+        K().attention_generic(q, pool, pool, bt, z, z, 1.0, 0, z[:1])
+
+
+# ------------------------------------------------------------------ cache write + attention
+def make_cache(n_seqs, lens, n_kv, d, page_size, dtype, seed, spare_pages=3):
+    """Pools filled with random keys and values for sequences of the given lengths, pages handed out
+    in a shuffled order; returns (k_pool, v_pool, block_table, k_dense, v_dense) with the dense copies
+    [seq][len, n_kv, d] in float32."""
+    rng = np.random.default_rng(seed)
+    g = torch.Generator(device=DEV).manual_seed(seed)
+    pages_per = [-(-n // page_size) for n in lens]
+    n_pages = sum(pages_per) + spare_pages
+    order = rng.permutation(n_pages).tolist()
+    max_pages = max(pages_per) + 1
+    bt = torch.full((n_seqs, max_pages), -1, dtype=torch.int32)
+    k_pool = torch.zeros(n_pages, n_kv, page_size, d, dtype=dtype, device=DEV)
+    v_pool = torch.zeros_like(k_pool)
+    k_dense, v_dense = [], []
+    for s, n in enumerate(lens):
+        k = torch.randn(n, n_kv, d, generator=g, device=DEV).to(dtype)
+        v = torch.randn(n, n_kv, d, generator=g, device=DEV).to(dtype)
+        for lp in range(pages_per[s]):
+            page = order.pop()
+            bt[s, lp] = page
+            lo, hi = lp * page_size, min(n, (lp + 1) * page_size)
+            k_pool[page, :, :hi - lo] = k[lo:hi].transpose(0, 1)
+            v_pool[page, :, :hi - lo] = v[lo:hi].transpose(0, 1)
+        k_dense.append(k.float()), v_dense.append(v.float())
+    return k_pool, v_pool, bt.to(DEV), k_dense, v_dense
+
+
+def ref_attention(q, k, v, pos, scale, window):
+    """One token: q [n_q, d] against keys [len, n_kv, d] up to `pos`, in float64."""
+    n_q, n_kv = q.shape[0], k.shape[1]
+    lo = max(0, pos - window + 1) if window else 0
+    out = torch.empty_like(q, dtype=torch.float64)
+    for h in range(n_q):
+        kh, vh = k[lo:pos + 1, h // (n_q // n_kv)].double(), v[lo:pos + 1, h // (n_q // n_kv)].double()
+        out[h] = torch.softmax(kh @ q[h].double() * scale, 0) @ vh
+    return out
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n_q,n_kv,d,page,window", [
+    (4, 4, 16, 16, 0), (5, 1, 48, 8, 0), (6, 1, 32, 16, 20), (8, 2, 128, 32, 0), (2, 1, 256, 16, 33),
+    (10, 2, 80, 64, 0)])
+def test_attention_generic(dtype, n_q, n_kv, d, page, window):
+    lens = [1, 37, 130, page, page + 1]
+    k_pool, v_pool, bt, kd, vd = make_cache(len(lens), lens, n_kv, d, page, dtype, seed=d + n_q)
+    # tokens: for each sequence its last position, plus some earlier ones (prefill-like rows)
+    toks = [(s, n - 1) for s, n in enumerate(lens)] + [(2, 0), (2, 31), (2, 32), (2, 63), (2, 64), (1, 19), (-1, 0)]
+    g = torch.Generator(device=DEV).manual_seed(7)
+    q = torch.randn(len(toks), n_q, d, generator=g, device=DEV).to(dtype)
+    slot = torch.tensor([s for s, _ in toks], dtype=torch.int32, device=DEV)
+    pos = torch.tensor([p for _, p in toks], dtype=torch.int32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    scale = 0.37
+    out = K().attention_generic(q, k_pool, v_pool, bt, pos, slot, scale, window, status).float().view(len(toks), n_q, d)
+    assert int(status.item()) == 0
+    for i, (s, p) in enumerate(toks):
+        if s < 0:
+            assert float(out[i].abs().sum()) == 0, "a padding row gives zeros"
+            continue
+        ref = ref_attention(q[i].float(), kd[s], vd[s], p, scale, window).float()
+        tol = dict(rtol=2e-2, atol=2e-2) if dtype == torch.bfloat16 else dict(rtol=1e-4, atol=1e-5)
+        torch.testing.assert_close(out[i], ref, **tol, msg=lambda m: f"token {i} (seq {s}, pos {p}): {m}")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attention_finds_one_far_key_among_hundreds(dtype):
+    """Scores are made so that one key far back takes all the weight: the output must be its value.
+    A kernel that drops a chunk, a page or the first or last key fails here, not in the noise."""
+    n_q, n_kv, d, page = 4, 2, 64, 16
+    n = 700
+    for far in (0, 1, 15, 16, 31, 32, 333, 698, 699):
+        k_pool, v_pool, bt, kd, vd = make_cache(1, [n], n_kv, d, page, dtype, seed=far)
+        q = torch.zeros(1, n_q, d, device=DEV)
+        for h in range(n_q):
+            q[0, h] = kd[0][far, h // 2] * 4.0          # aligned with key `far`: score ~ 4 |k|^2 against ~ N(0, 4|k|)
+        q = q.to(dtype)
+        z = torch.zeros(1, dtype=torch.int32, device=DEV)
+        out = K().attention_generic(q, k_pool, v_pool, bt, torch.tensor([n - 1], dtype=torch.int32, device=DEV), z,
+                                    1.0, 0, z.clone()).float().view(n_q, d)
+        for h in range(n_q):
+            torch.testing.assert_close(out[h], vd[0][far, h // 2], rtol=2e-2, atol=2e-2,
+                                       msg=lambda m: f"far key {far}, head {h}: {m}")
+        # with a window that ends just short of it the far key must be gone
+        if far < n - 40:
+            out_w = K().attention_generic(q, k_pool, v_pool, bt, torch.tensor([n - 1], dtype=torch.int32, device=DEV),
+                                          z, 1.0, n - 1 - far, z.clone()).float().view(n_q, d)
+            assert float((out_w[0] - vd[0][far, 0]).abs().max()) > 0.1
+            out_in = K().attention_generic(q, k_pool, v_pool, bt, torch.tensor([n - 1], dtype=torch.int32, device=DEV),
+                                           z, 1.0, n - far, z.clone()).float().view(n_q, d)
+            torch.testing.assert_close(out_in[0], vd[0][far, 0], rtol=2e-2, atol=2e-2)
+
+
+def test_attention_generic_same_bits_in_any_batch_and_any_pages():
+    n_q, n_kv, d, page = 6, 2, 32, 16
+    lens = [90, 300]
+    a = make_cache(2, lens, n_kv, d, page, torch.float32, seed=1)
+    b = make_cache(2, lens, n_kv, d, page, torch.float32, seed=1, spare_pages=9)     # same numbers, other pages
+    g = torch.Generator(device=DEV).manual_seed(8)
+    q = torch.randn(5, n_q, d, generator=g, device=DEV)
+    slot = torch.tensor([0, 1, 1, 0, 1], dtype=torch.int32, device=DEV)
+    pos = torch.tensor([89, 299, 17, 40, 128], dtype=torch.int32, device=DEV)
+    st = torch.zeros(1, dtype=torch.int32, device=DEV)
+    whole = K().attention_generic(q, a[0], a[1], a[2], pos, slot, 0.2, 0, st)
+    other = K().attention_generic(q, b[0], b[1], b[2], pos, slot, 0.2, 0, st)
+    assert torch.equal(whole, other), "where the pages lie must not matter"
+    for i in range(5):
+        one = K().attention_generic(q[i:i + 1].contiguous(), a[0], a[1], a[2], pos[i:i + 1].contiguous(),
+                                    slot[i:i + 1].contiguous(), 0.2, 0, st)
+        assert torch.equal(whole[i:i + 1], one), "a token's result must not depend on the batch"
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n_q,n_kv,d,rot,qk_norm,wdt", [
+    (4, 2, 16, 16, True, torch.bfloat16), (6, 1, 32, 32, True, torch.float32), (5, 5, 48, 48, True, torch.float32),
+    (3, 1, 64, 32, True, torch.float32), (2, 2, 128, 128, False, torch.float32), (2, 1, 80, 0, False, torch.float32)])
+def test_qk_norm_rope_append(dtype, n_q, n_kv, d, rot, qk_norm, wdt):
+    import plain_qwen3 as plain
+    from garlic_inference_b200.parts.rotary import RotaryPositions
+    page, n_pages, max_pages, max_pos, theta, eps = 8, 12, 6, 48, 1e4, 1e-5
+    g = torch.Generator(device=DEV).manual_seed(d)
+    toks = [(0, 0), (0, 1), (0, 7), (0, 8), (1, 30), (-1, 3), (1, 31), (1, 32)]
+    n = len(toks)
+    qkv = torch.randn(n, (n_q + 2 * n_kv) * d, generator=g, device=DEV).to(dtype)
+    qw = (1 + 0.2 * torch.randn(d, generator=g, device=DEV)).to(wdt) if qk_norm else None
+    kw = (1 + 0.2 * torch.randn(d, generator=g, device=DEV)).to(wdt) if qk_norm else None
+    if rot:
+        cos, sin = (t.to(DEV) for t in RotaryPositions.build_tables(rot, theta, max_pos))
+    else:
+        cos = sin = torch.zeros(max_pos, 0, device=DEV)
+    bt = torch.tensor([[3, 9, -1, -1, -1, -1], [0, 1, 2, 11, 5, -1]], dtype=torch.int32, device=DEV)
+    k_pool = torch.zeros(n_pages, n_kv, page, d, dtype=dtype, device=DEV)
+    v_pool = torch.zeros_like(k_pool)
+    slot = torch.tensor([s for s, _ in toks], dtype=torch.int32, device=DEV)
+    pos = torch.tensor([p for _, p in toks], dtype=torch.int32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    q_out = K().qk_norm_rope_append(qkv, n_q, n_kv, d, qw, kw, eps, cos, sin, rot, pos, slot, k_pool, v_pool, bt, status)
+    assert int(status.item()) == 0
+
+    x = qkv.float().cpu()
+    q_ref = x[:, :n_q * d].view(n, n_q, d)
+    k_ref = x[:, n_q * d:(n_q + n_kv) * d].view(n, n_kv, d)
+    v_ref = x[:, (n_q + n_kv) * d:].view(n, n_kv, d)
+    if qk_norm:
+        q_ref = plain.rms_norm(q_ref, qw.float().cpu(), eps)
+        k_ref = plain.rms_norm(k_ref, kw.float().cpu(), eps)
+    if rot:
+        pcpu = pos.cpu()
+        q_ref = torch.cat([plain.apply_rope(q_ref[..., :rot], pcpu, theta), q_ref[..., rot:]], -1)
+        k_ref = torch.cat([plain.apply_rope(k_ref[..., :rot], pcpu, theta), k_ref[..., rot:]], -1)
+    tol = ulp_tol(dtype) if dtype == torch.bfloat16 else dict(rtol=1e-5, atol=1e-5)
+    torch.testing.assert_close(q_out.float().cpu(), q_ref.to(dtype).float(), **tol)
+    written = torch.zeros(n_pages, page, dtype=torch.bool)
+    for i, (s, p) in enumerate(toks):
+        if s < 0:
+            continue
+        pg, off = int(bt[s, p // page]), p % page
+        written[pg, off] = True
+        torch.testing.assert_close(k_pool[pg, :, off].float().cpu(), k_ref[i].to(dtype).float(), **tol)
+        assert torch.equal(v_pool[pg, :, off].cpu(), v_ref[i].to(dtype)), "values are copied as they are"
+    untouched = ~written.view(n_pages, 1, page, 1).expand(-1, n_kv, -1, d)
+    assert float(k_pool.float().cpu()[untouched].abs().sum()) == 0 and float(v_pool.float().cpu()[untouched].abs().sum()) == 0
+
+    # a reader of another layer's cache: q as before, nothing written
+    k2, v2 = torch.zeros_like(k_pool), torch.zeros_like(v_pool)
+    q2 = K().qk_norm_rope_append(qkv, n_q, n_kv, d, qw, kw, eps, cos, sin, rot, pos, slot, k2, v2, bt, status, append=False)
+    assert torch.equal(q2, q_out) and float(k2.float().abs().sum()) == 0 and float(v2.float().abs().sum()) == 0
+
+
+def test_out_of_range_indices_set_the_status_and_touch_nothing():
+    n_q, n_kv, d, page = 2, 1, 16, 8
+    qkv = torch.ones(2, (n_q + 2) * d, device=DEV)
+    cos = sin = torch.zeros(16, d // 2, device=DEV)
+    bt = torch.tensor([[0, -1]], dtype=torch.int32, device=DEV)
+    pool = torch.zeros(2, n_kv, page, d, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    slot = torch.zeros(2, dtype=torch.int32, device=DEV)
+    pos = torch.tensor([3, 9], dtype=torch.int32, device=DEV)           # position 9 lies on an unmapped page
+    K().qk_norm_rope_append(qkv, n_q, n_kv, d, None, None, 1e-6, cos, sin, d, pos, slot, pool, pool.clone(), bt, status)
+    assert int(status.item()) == 2
+    assert float(pool[1].abs().sum()) == 0
+
+
+# ------------------------------------------------------------------ sampling
+def test_greedy_takes_the_lowest_of_equal_maxima():
+    logits = torch.full((4, 5003), -1.0, device=DEV)
+    logits[0, [4000, 77, 5002]] = 3.0
+    logits[1, 5002] = 9.0
+    logits[2, 0] = 0.5
+    logits[3] = float("-inf")
+    out = K().sample(logits, None, None, None, 0)
+    assert out.tolist() == [77, 5002, 0, 0]
+    view = torch.zeros(3, 100, device=DEV)
+    view[:, 7] = 1.0
+    assert K().sample(view[:, :50], None, None, None, 0).tolist() == [7, 7, 7]      # rows with a stride
+
+
+def test_temperature_draws_follow_the_softmax_and_the_key():
+    vocab, n = 11, 20000
+    g = torch.Generator(device=DEV).manual_seed(9)
+    row = torch.randn(vocab, generator=g, device=DEV) * 2
+    logits = row.expand(n, vocab).contiguous()
+    temps = torch.full((n,), 0.7, device=DEV)
+    streams = torch.arange(n, dtype=torch.int64, device=DEV)
+    counters = torch.zeros(n, dtype=torch.int32, device=DEV)
+    draws = K().sample(logits, temps, streams, counters, 1234)
+    freq = torch.bincount(draws.long(), minlength=vocab).float().cpu() / n
+    p = torch.softmax(row.cpu() / 0.7, 0)
+    assert float((freq - p).abs().max()) < 4 * math.sqrt(0.25 / n) + 1e-3
+    assert torch.equal(draws, K().sample(logits, temps, streams, counters, 1234)), "same key, same draw"
+    assert not torch.equal(draws, K().sample(logits, temps, streams, counters, 1235))
+    # a row's draw depends on its key (seed, stream, counter) only, not on its place in the batch
+    perm = torch.randperm(n, device=DEV)
+    again = K().sample(logits, temps, streams[perm].contiguous(), counters, 1234)
+    assert torch.equal(again, draws[perm])
+    # the kernel's generator is the documented one
+    from garlic_inference_b200.ops import lib
+    u = lib().gi_sample_uniform(1234, 5, 0, 3)
+    z = logits[5].cpu() / 0.7 - torch.log(-torch.log(torch.tensor(
+        [lib().gi_sample_uniform(1234, 5, 0, i) for i in range(vocab)])))
+    assert 0.0 < u < 1.0 and int(z.argmax()) == int(draws[5])
+    # temperature 0 in a mixed batch is greedy
+    temps[:10] = 0.0
+    mixed = K().sample(logits, temps, streams, counters, 1234)
+    assert mixed[:10].tolist() == [int(row.argmax())] * 10 and torch.equal(mixed[10:], draws[10:])

@@ -1,0 +1,161 @@
+"""The engine against the plain implementation, in float32 and in bfloat16: every request alone and
+whole; with the last 32 tokens one by one; in batches of unequal lengths whose shorter requests end
+earlier, one batch after another in a cache too small to hold them all at once (slots and pages are
+used again); long decoding; the first tokens of a sequence."""
+import numpy as np
+import pytest
+import torch
+
+import tiny
+
+pytestmark = pytest.mark.gpu
+
+LENGTHS = {
+    "A": [7, 128, 33, 64, 1, 65, 100],
+    "B": [5, 11, 2, 300, 97, 64, 129],
+    "C": [90, 41, 40, 200, 17, 3, 130],
+}
+BATCHES = [["r0", "r1", "r2"], ["r3", "r4"], ["r5", "r6"]]
+
+
+def _round64(n):
+    return -(-n // 64) * 64
+
+
+@pytest.fixture(scope="module")
+def plain_cache(model_dirs):
+    made = {}
+
+    def get(name):
+        if name not in made:
+            vocab = tiny.TINY[name]["cfg"]["vocab_size"]
+            reqs = tiny.random_requests(vocab, LENGTHS[name], seed=ord(name))
+            made[name] = (reqs, tiny.plain_logits(model_dirs(name), reqs))
+        return made[name]
+
+    return get
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_every_cutting_agrees_with_the_plain_implementation(name, dtype, gpu_models, plain_cache):
+    reqs, want = plain_cache(name)
+    tol = tiny.TOL[dtype]
+    # a cache that holds the largest batch and no more: later batches must reuse slots and pages
+    max_tokens = max(sum(_round64(len(reqs[r])) for r in b) for b in BATCHES)
+    model = gpu_models(name, dtype, max_tokens=max_tokens, page_size=16)
+
+    whole = tiny.run_trace_in_process(model, tiny.trace_whole(reqs))
+    tiny.assert_covers(whole, reqs)
+    tiny.compare(whole, want, tol, f"{name} {dtype} whole")
+
+    tail = tiny.run_trace_in_process(model, tiny.trace_tail_by_one(reqs, tail=32))
+    tiny.assert_covers(tail, reqs)
+    tiny.compare(tail, want, tol, f"{name} {dtype} last 32 one by one")
+
+    batched = tiny.run_trace_in_process(model, tiny.trace_batched(reqs, BATCHES, prompt_frac=0.5))
+    tiny.assert_covers(batched, reqs)
+    tiny.compare(batched, want, tol, f"{name} {dtype} unequal batches")
+
+    cache = model.engine.cache
+    assert cache.slots.n_free == cache.max_slots
+    assert all(g.host.pool.n_free == g.host.pool.n_pages for g in cache.groups), "a page was lost"
+
+    if dtype == "float32":
+        # the float32 kernels sum in an order that depends on the position alone: the three cuttings
+        # give the same bits, not merely the same numbers up to rounding
+        for rid in reqs:
+            for p in range(len(reqs[rid])):
+                assert np.array_equal(whole[rid][p], tail[rid][p]), f"{name}: {rid} position {p}: whole vs one by one"
+                assert np.array_equal(whole[rid][p], batched[rid][p]), f"{name}: {rid} position {p}: whole vs batched"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_float32_is_far_closer_than_bfloat16(dtype, gpu_models, plain_cache):
+    """The float32 path is a true 32-bit path: its error is orders of magnitude below bfloat16's."""
+    reqs, want = plain_cache("B")
+    model = gpu_models("B", dtype, max_tokens=4096, page_size=16)
+    got = tiny.run_trace_in_process(model, tiny.trace_whole({"r3": reqs["r3"]}))
+    worst = tiny.compare(got, want, tiny.TOL[dtype], f"B {dtype}")
+    if dtype == "float32":
+        assert worst < 2e-5
+    else:
+        assert worst > 2e-5, "bfloat16 cannot be this exact: is the float32 path running instead?"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name,n_prompt,n_total", [("B", 10, 640), ("C", 3, 300)])
+def test_long_decoding(name, n_prompt, n_total, dtype, gpu_models, model_dirs):
+    vocab = tiny.TINY[name]["cfg"]["vocab_size"]
+    reqs = tiny.random_requests(vocab, [n_total], seed=11)
+    want = tiny.plain_logits(model_dirs(name), reqs)
+    model = gpu_models(name, dtype, max_tokens=4096, page_size=16)
+    steps = tiny.trace_tail_by_one(reqs, tail=n_total - n_prompt)
+    got = tiny.run_trace_in_process(model, steps)
+    tiny.assert_covers(got, reqs)
+    tiny.compare(got, want, tiny.TOL[dtype], f"{name} {dtype} decoding {n_total - n_prompt} tokens")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_first_tokens_of_a_sequence(name, dtype, gpu_models, model_dirs):
+    vocab = tiny.TINY[name]["cfg"]["vocab_size"]
+    reqs = tiny.random_requests(vocab, [1, 2, 3, 1], seed=12)
+    want = tiny.plain_logits(model_dirs(name), reqs)
+    model = gpu_models(name, dtype, max_tokens=4096, page_size=16)
+    for steps in (tiny.trace_whole(reqs), tiny.trace_tail_by_one(reqs, tail=32),
+                  tiny.trace_batched(reqs, [["r0", "r1", "r2", "r3"]], prompt_frac=0.0)):
+        got = tiny.run_trace_in_process(model, steps)
+        tiny.assert_covers(got, reqs)
+        tiny.compare(got, want, tiny.TOL[dtype], f"{name} {dtype} first tokens")
+
+
+def test_padding_rows_change_nothing(gpu_models, plain_cache):
+    """Rows with slot -1 may ride along in a step (a padded batch): the others' logits keep their bits."""
+    from garlic_inference_b200.parts import StepContext
+    reqs, _ = plain_cache("A")
+    model = gpu_models("A", "float32", max_tokens=4096, page_size=16)
+    eng = model.engine
+    toks = reqs["r2"]
+
+    def run(pad):
+        s = eng.alloc_slot()
+        n = len(toks)
+        eng.cache.prepare([s], [n])
+        t = torch.tensor(toks + [0] * pad, dtype=torch.int32, device="cuda")
+        pos = torch.tensor(list(range(n)) + [0] * pad, dtype=torch.int32, device="cuda")
+        slot = torch.tensor([s] * n + [-1] * pad, dtype=torch.int32, device="cuda")
+        ctx = StepContext(n_tokens=n + pad, tokens=t, tok_pos=pos, tok_slot=slot, seq_slots=[s], seq_starts=[0],
+                          seq_lens=[n], seq_past=[0], max_kv_len=n, status=eng.cache.status)
+        rows = torch.arange(n, dtype=torch.int32, device="cuda")
+        out = model.model.forward(ctx, eng.cache, rows).cpu()
+        eng.cache.commit([s], [n])
+        eng.free_slot(s)
+        return out
+
+    plain_run, padded = run(0), run(5)
+    assert torch.equal(plain_run, padded)
+    eng.check()
+
+
+def test_step_errors_come_before_any_launch(gpu_models):
+    from garlic_inference_b200.cache import CacheError
+    from garlic_inference_b200.engine import StepEntry, StepError
+    model = gpu_models("A", "float32", max_tokens=128, page_size=16)
+    s = model.alloc_slot()
+    try:
+        with pytest.raises(StepError, match="outside the vocabulary"):
+            model.step([StepEntry(s, [1, 512], [0])])
+        with pytest.raises(StepError, match="want index"):
+            model.step([StepEntry(s, [1, 2], [2])])
+        with pytest.raises(StepError, match="no tokens"):
+            model.step([StepEntry(s, [], [])])
+        with pytest.raises(CacheError, match="limit is 128"):
+            model.step([StepEntry(s, [1] * 129, [])])
+        assert model.engine.cache.length(s) == 0
+        assert model.step([StepEntry(s, [1, 2, 3], [])]) is None          # nothing wanted: nothing returned
+        assert model.engine.cache.length(s) == 3
+        out = model.step([StepEntry(s, [4], [0])])
+        assert out.shape == (1, 512) and out.dtype == torch.float32
+    finally:
+        model.free_slot(s)

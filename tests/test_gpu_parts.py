@@ -1,0 +1,323 @@
+"""Each part of a layer alone against the plain implementation's function for it, and the generality
+of the assembly: a toy mixer with state of its own (defined here, registered here, no file of the
+package changed), different mixers in different layers, a layer named twice in the schedule, and a
+layer that reads another layer's cache."""
+import json
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen3 as plain
+import tiny
+
+pytestmark = pytest.mark.gpu
+
+DEV = torch.device("cuda", 0)
+
+
+class DictLoader:
+    """Hands a part its tensors from a dict, the way the model builder's loader does."""
+
+    def __init__(self, tensors, rt):
+        from garlic_inference_b200.weights import device_dtype
+        self.t, self.rt, self._dd = tensors, rt, device_dtype
+
+    def dtype(self, local):
+        return self._dd(self.t[local].dtype, self.rt.dtype)
+
+    def __call__(self, local, out=None):
+        if out is not None:
+            out.copy_(self.t[local])
+            return out
+        return self.t[local].to(device=self.rt.device, dtype=self.dtype(local)).contiguous()
+
+
+def rt_for(dtype):
+    from garlic_inference_b200.parts import Runtime
+    return Runtime(dtype, DEV)
+
+
+def rnd(shape, seed, scale=1.0, dtype=torch.bfloat16):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).to(dtype)
+
+
+def tol(dtype):
+    return dict(rtol=3e-2, atol=3e-2) if dtype == torch.bfloat16 else dict(rtol=1e-4, atol=1e-5)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_rms_norm_part(dtype):
+    from garlic_inference_b200.parts import RMSNorm
+    w = 1 + rnd((200,), 0, 0.2)
+    part = RMSNorm(dict(size=200, eps=1e-4), DictLoader({"weight": w}, rt_for(dtype)), rt_for(dtype))
+    res = rnd((6, 200), 1, 2.0, torch.float32).to(DEV)
+    delta = rnd((6, 200), 2, 1.0, dtype).to(DEV)
+    want = plain.rms_norm(res.cpu() + delta.float().cpu(), w.float(), 1e-4)
+    got = part.add_norm(delta, res)
+    torch.testing.assert_close(got.float().cpu(), want, **tol(dtype))
+
+
+def test_rotary_part_tables():
+    from garlic_inference_b200.parts import RotaryPositions
+    part = RotaryPositions(dict(head_dim=48, rotary_dim=48, theta=5e5, max_positions=4000), None, rt_for(torch.float32))
+    cos, sin, r = part.rotary_tables()
+    ang = plain.rope_angles(torch.arange(4000), 48, 5e5, torch.float64)
+    assert r == 48 and cos.shape == (4000, 24)
+    torch.testing.assert_close(cos.cpu().double(), ang.cos(), rtol=0, atol=1e-7)
+    torch.testing.assert_close(sin.cpu().double(), ang.sin(), rtol=0, atol=1e-7)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_swiglu_part(dtype):
+    from garlic_inference_b200.parts import SwiGLUMLP
+    w = {"gate_proj": rnd((112, 80), 3, 0.1), "up_proj": rnd((112, 80), 4, 0.1), "down_proj": rnd((80, 112), 5, 0.1)}
+    part = SwiGLUMLP(dict(hidden_size=80, intermediate_size=112), DictLoader(w, rt_for(dtype)), rt_for(dtype))
+    x = rnd((13, 80), 6, 1.0, dtype)
+    want = plain.swiglu_mlp(x.float(), {"p." + k + ".weight": v.float() for k, v in w.items()}, "p.")
+    got = part.step(x.to(DEV), None)
+    torch.testing.assert_close(got.float().cpu(), want, **tol(dtype))
+
+
+def _attention_setup(dtype, window, n_q=6, n_kv=2, d=32, hidden=96, S=50, page=16):
+    from garlic_inference_b200.cache import PagedCache
+    from garlic_inference_b200.parts import GQAAttention, RotaryPositions, StepContext
+    rt = rt_for(dtype)
+    w = {"q_proj": rnd((n_q * d, hidden), 10, 0.1), "k_proj": rnd((n_kv * d, hidden), 11, 0.1),
+         "v_proj": rnd((n_kv * d, hidden), 12, 0.1), "o_proj": rnd((hidden, n_q * d), 13, 0.1),
+         "q_norm": 1 + rnd((d,), 14, 0.2), "k_norm": 1 + rnd((d,), 15, 0.2)}
+    params = dict(hidden_size=hidden, n_heads=n_q, n_kv_heads=n_kv, head_dim=d, qk_norm=True, qk_norm_eps=1e-5,
+                  window=window, softmax_scale=d ** -0.5)
+    part = GQAAttention(params, DictLoader(w, rt), rt)
+    rope = RotaryPositions(dict(head_dim=d, theta=1e4, max_positions=256), None, rt)
+    cache = PagedCache([part.cache_requirement()], max_tokens=256, max_positions=256, dtype=dtype, device=DEV,
+                       page_size=page)
+    x = rnd((S, hidden), 16, 1.0, dtype)
+    cfg = dict(num_attention_heads=n_q, num_key_value_heads=n_kv, head_dim=d, rms_norm_eps=1e-5, rope_theta=1e4)
+    want = plain.attention_block(x.float(), {"a." + k + ".weight": v.float() for k, v in w.items()}, "a.", cfg,
+                                 torch.arange(S), window)
+
+    def ctx_for(slot, lo, hi):
+        n = hi - lo
+        return StepContext(n_tokens=n, tokens=torch.zeros(n, dtype=torch.int32, device=DEV),
+                           tok_pos=torch.arange(lo, hi, dtype=torch.int32, device=DEV),
+                           tok_slot=torch.full((n,), slot, dtype=torch.int32, device=DEV),
+                           seq_slots=[slot], seq_starts=[0], seq_lens=[n], seq_past=[lo], all_single=(n == 1),
+                           max_kv_len=hi, status=cache.status)
+    return part, rope, cache, x.to(DEV), want, ctx_for
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("window", [None, 9])
+def test_attention_part_whole_and_in_pieces(dtype, window):
+    part, rope, cache, x, want, ctx_for = _attention_setup(dtype, window)
+    S = x.shape[0]
+    s = cache.alloc_slot()
+    cache.prepare([s], [S])
+    got = part.step(x, ctx_for(s, 0, S), cache.view(0), rope)
+    cache.commit([s], [S])
+    torch.testing.assert_close(got.float().cpu(), want, **tol(dtype))
+    cache.free_slot(s)
+    # the same in pieces of 17, 1, 1, ... from the cache
+    s = cache.alloc_slot()
+    outs, lo = [], 0
+    for n in [17] + [1] * (S - 17):
+        cache.prepare([s], [n])
+        outs.append(part.step(x[lo:lo + n].contiguous(), ctx_for(s, lo, lo + n), cache.view(0), rope))
+        cache.commit([s], [n])
+        lo += n
+    torch.testing.assert_close(torch.cat(outs).float().cpu(), want, **tol(dtype))
+    cache.check_status()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_block_embedding_and_head_parts(dtype, model_dirs):
+    """A whole pre-norm block of configuration B, then the two ends of the model, each alone."""
+    from garlic_inference_b200.engine import DecoderModel
+    from garlic_inference_b200.cache import PagedCache
+    from garlic_inference_b200.parts import StepContext
+    from garlic_inference_b200.weights import Checkpoint
+    cfg_obj = tiny.make_config("B")
+    d = model_dirs("B")
+    cfg, w = plain.read_model_dir(d)
+    model = DecoderModel(cfg_obj.plan(), Checkpoint(d), rt_for(dtype))
+    ids = np.random.default_rng(5).integers(0, 1000, size=21)
+    S = len(ids)
+    cache = PagedCache(model.cache_requirements(), max_tokens=64, max_positions=640, dtype=dtype, device=DEV, page_size=16)
+    s = cache.alloc_slot()
+    cache.prepare([s], [S])
+    ctx = StepContext(n_tokens=S, tokens=torch.tensor(ids, dtype=torch.int32, device=DEV),
+                      tok_pos=torch.arange(S, dtype=torch.int32, device=DEV),
+                      tok_slot=torch.full((S,), s, dtype=torch.int32, device=DEV), seq_slots=[s], seq_starts=[0],
+                      seq_lens=[S], seq_past=[0], max_kv_len=S, status=cache.status)
+    residual = model.embedding.step(ctx)
+    h0 = plain.embed(torch.tensor(ids), w["model.embed_tokens.weight"])
+    assert torch.equal(residual.cpu(), h0)
+    delta = model.blocks[1].step(None, residual, ctx, cache.view(1), True)
+    h1 = plain.decoder_layer(h0, w, 1, cfg, torch.arange(S))
+    torch.testing.assert_close(residual.cpu() + delta.float().cpu(), h1, **tol(dtype))
+    rows = torch.tensor([S - 1, 0], dtype=torch.int32, device=DEV)
+    normed = model.final_norm.add_norm(delta, residual, rows=rows)
+    logits = model.head.step(normed)
+    want = plain.output_head(h1[[S - 1, 0]], w, cfg)
+    assert logits.dtype == torch.float32
+    torch.testing.assert_close(logits.cpu(), want, **tol(dtype))
+    cache.check_status()
+
+
+# ---------------------------------------------------------------------------------------------------
+# generality: a toy mixer with state, registered from outside; layer order as data
+# ---------------------------------------------------------------------------------------------------
+def _toy_classes():
+    """A mixer whose only memory is a running sum of its inputs per sequence, kept in the cache's
+    fixed-size state region, and a configuration that alternates it with attention."""
+    from garlic_inference_b200 import Qwen3Config, register_architecture, register_part
+    from garlic_inference_b200.cache import StateRequirement
+    from garlic_inference_b200.config import ScheduleEntry
+    from garlic_inference_b200.config.base import PartSpec
+    from garlic_inference_b200.parts import Mixer
+    from garlic_inference_b200.weights import TensorWant
+    import dataclasses
+
+    class RunningSumMixer(Mixer):
+        kind = "toy_running_sum"
+
+        @classmethod
+        def wanted(cls, params):
+            return {"mix": TensorWant((params["hidden_size"],), "norm")}
+
+        def __init__(self, params, load, rt):
+            super().__init__(params, load, rt)
+            self.hidden = params["hidden_size"]
+            self.decay = params["decay"]
+            self.mix = load("mix").float()
+
+        def cache_requirement(self):
+            return StateRequirement((self.hidden,), torch.float32)
+
+        def step(self, x, ctx, cache, position, writes_cache=True):
+            out = torch.empty_like(x)
+            for slot, start, n in zip(ctx.seq_slots, ctx.seq_starts, ctx.seq_lens):
+                state = cache.state[slot]
+                for t in range(start, start + n):                 # tokens of a sequence in order
+                    state = state * self.decay + x[t].float()
+                    out[t] = (state * self.mix).to(x.dtype)
+                cache.state[slot] = state
+            return out
+
+    class ToyConfig(Qwen3Config):
+        def plan(self):
+            base = super().plan()
+            layers = list(base.layers)
+            for i in range(1, len(layers), 2):
+                toy = PartSpec("toy_running_sum", dict(hidden_size=self.hidden_size, decay=0.9),
+                               dict(mix=f"model.layers.{i}.toy.mix"))
+                layers[i] = dataclasses.replace(layers[i], mixer=toy, position=None)
+            return dataclasses.replace(base, architecture="ToyStateForCausalLM", layers=tuple(layers))
+
+    register_part("toy_running_sum", RunningSumMixer)
+    register_architecture("ToyStateForCausalLM", ToyConfig)
+    return ToyConfig
+
+
+def _plain_toy_forward(cfg, w, ids):
+    ids = torch.as_tensor(ids)
+    pos = torch.arange(len(ids))
+    h = plain.embed(ids, w["model.embed_tokens.weight"])
+    for i in range(cfg["num_hidden_layers"]):
+        p = f"model.layers.{i}."
+        if i % 2 == 0:
+            h = plain.decoder_layer(h, w, i, cfg, pos)
+            continue
+        x = plain.rms_norm(h, w[p + "input_layernorm.weight"], cfg["rms_norm_eps"])
+        state, mixed = torch.zeros(cfg["hidden_size"]), []
+        for t in range(len(ids)):
+            state = state * 0.9 + x[t]
+            mixed.append(state * w[p + "toy.mix"])
+        r = torch.stack(mixed) + h
+        x = plain.rms_norm(r, w[p + "post_attention_layernorm.weight"], cfg["rms_norm_eps"])
+        h = plain.swiglu_mlp(x, w, p + "mlp.") + r
+    return plain.output_head(h, w, cfg)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_toy_mixer_with_state_is_registered_built_and_stepped(dtype, tmp_path):
+    from garlic_inference_b200 import AutoModel, write_random_model
+    ToyConfig = _toy_classes()
+    cfg_obj = ToyConfig(**{**tiny.TINY["B"]["cfg"], "num_hidden_layers": 4, "architectures": ["ToyStateForCausalLM"]})
+    d = write_random_model(tmp_path / "toy", cfg_obj, seed=3, std=0.05, norm_std=0.2)
+    assert json.loads((d / "config.json").read_text())["architectures"] == ["ToyStateForCausalLM"]
+    model = AutoModel.from_pretrained(d, device=0, dtype=dtype, max_tokens=512, page_size=16)
+    assert type(model.config) is ToyConfig
+    cache = model.engine.cache
+    assert cache.state_bytes_per_slot == 2 * 96 * 4 and len(cache.groups) == 1 and len(cache.groups[0].entries) == 2
+    cfg, w = plain.read_model_dir(d)
+    reqs = tiny.random_requests(1000, [40, 9, 70, 33], seed=21)
+    want = {rid: _plain_toy_forward(cfg, w, t).numpy() for rid, t in reqs.items()}
+    for steps in (tiny.trace_whole(reqs), tiny.trace_tail_by_one(reqs, tail=32),
+                  tiny.trace_batched(reqs, [["r0", "r1"], ["r2", "r3"]])):       # slots, and their state, used again
+        got = tiny.run_trace_in_process(model, steps)
+        tiny.assert_covers(got, reqs)
+        tiny.compare(got, want, tiny.TOL[dtype], f"toy {dtype}")
+
+
+def _plain_layer(h, w, i, cfg, pos, kv=None):
+    """plain.decoder_layer with the keys and values handed in (a reader of another layer's cache)
+    or handed out."""
+    p = f"model.layers.{i}."
+    a = p + "self_attn."
+    n_q, n_kv, d, eps, theta = (cfg[k] for k in ("num_attention_heads", "num_key_value_heads", "head_dim",
+                                                 "rms_norm_eps", "rope_theta"))
+    S = h.shape[0]
+    x = plain.rms_norm(h, w[p + "input_layernorm.weight"], eps)
+    q = plain.apply_rope(plain.rms_norm((x @ w[a + "q_proj.weight"].T).view(S, n_q, d), w[a + "q_norm.weight"], eps), pos, theta)
+    if kv is None:
+        k = plain.apply_rope(plain.rms_norm((x @ w[a + "k_proj.weight"].T).view(S, n_kv, d), w[a + "k_norm.weight"], eps), pos, theta)
+        v = (x @ w[a + "v_proj.weight"].T).view(S, n_kv, d)
+        kv = (k, v)
+    o = plain.attention_scores(q, kv[0], kv[1]).reshape(S, n_q * d) @ w[a + "o_proj.weight"].T
+    r = o + h
+    x = plain.rms_norm(r, w[p + "post_attention_layernorm.weight"], eps)
+    return plain.swiglu_mlp(x, w, p + "mlp.") + r, kv
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_layer_order_is_data(dtype, tmp_path):
+    """Schedule: layer 0, layer 1, layer 0 again (its weights shared, a cache entry of its own), then
+    layer 2 reading the cache that layer 1 wrote."""
+    import dataclasses
+    from garlic_inference_b200 import AutoModel, Qwen3Config, register_architecture, write_random_model
+    from garlic_inference_b200.config import ScheduleEntry
+
+    class LoopedConfig(Qwen3Config):
+        def plan(self):
+            base = super().plan()
+            sched = (ScheduleEntry(0, 0), ScheduleEntry(1, 1), ScheduleEntry(0, 2), ScheduleEntry(2, 1, writes_cache=False))
+            return dataclasses.replace(base, schedule=sched)
+
+    register_architecture("LoopedForCausalLM", LoopedConfig)
+    cfg_obj = LoopedConfig(**{**tiny.TINY["A"]["cfg"], "num_hidden_layers": 3, "architectures": ["LoopedForCausalLM"]})
+    d = write_random_model(tmp_path / "looped", cfg_obj, seed=4, std=0.05, norm_std=0.2)
+    model = AutoModel.from_pretrained(d, device=0, dtype=dtype, max_tokens=512, page_size=16)
+    assert len(model.engine.cache.groups[0].entries) == 3
+    cfg, w = plain.read_model_dir(d)
+
+    def plain_forward(ids):
+        ids = torch.as_tensor(ids)
+        pos = torch.arange(len(ids))
+        h = plain.embed(ids, w["model.embed_tokens.weight"])
+        h, _ = _plain_layer(h, w, 0, cfg, pos)
+        h, kv1 = _plain_layer(h, w, 1, cfg, pos)
+        h, _ = _plain_layer(h, w, 0, cfg, pos)
+        h, _ = _plain_layer(h, w, 2, cfg, pos, kv=kv1)
+        return plain.output_head(h, w, cfg)
+
+    reqs = tiny.random_requests(512, [50, 7, 90], seed=22)
+    want = {rid: plain_forward(t).numpy() for rid, t in reqs.items()}
+    for steps in (tiny.trace_whole(reqs), tiny.trace_tail_by_one(reqs, tail=32),
+                  tiny.trace_batched(reqs, [["r0", "r1", "r2"]])):
+        got = tiny.run_trace_in_process(model, steps)
+        tiny.assert_covers(got, reqs)
+        tiny.compare(got, want, tiny.TOL[dtype], f"looped {dtype}")
