@@ -222,14 +222,14 @@ def main() -> int:
     # ---- the same through the entry point: host ids in, host ids out, every step ------------------
     prompts = [random_prompt(CACHED) for _ in range(args.batch)]
     model.generate(prompts[:1], max_new_tokens=4)                           # warm the path
-    up0 = eng._staging.bytes_uploaded
+    up0 = eng.bytes_uploaded
     clocks.start()
     out = model.generate(prompts, max_new_tokens=K + 1)
     clocks.stop()
     st = model.last_stats
     e2e_steps = st.steps - 1
     e2e = {"value": args.batch * e2e_steps / st.decode_seconds, "unit": "tokens/s",
-           "h2d_bytes_per_step": (eng._staging.bytes_uploaded - up0) / st.steps,
+           "h2d_bytes_per_step": (eng.bytes_uploaded - up0) / st.steps,
            "d2h_bytes_per_step": 4 * args.batch}
     assert all(len(o) == K + 1 for o in out)
 

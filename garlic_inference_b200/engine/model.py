@@ -92,6 +92,12 @@ class DecoderModel:
                 raise IndexError(f"the schedule names layer {e.layer}; the plan has {len(self.blocks)}")
         self.vocab_size, self.hidden_size, self.max_positions = plan.vocab_size, plan.hidden_size, plan.max_positions
 
+    @property
+    def graph_safe(self) -> bool:
+        """True if every part allows a decode step to be recorded into a CUDA graph."""
+        return all(p.graph_safe for p in (self.embedding, *self.positions.values(), *self.blocks,
+                                          self.final_norm, self.head))
+
     def cache_requirements(self) -> list:
         """What each cache entry has to hold; entries shared by several runs must agree."""
         reqs: list = [None] * self.plan.n_cache_entries()

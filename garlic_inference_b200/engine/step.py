@@ -74,7 +74,7 @@ class Engine:
     """A model, its cache, and the step function over them."""
 
     def __init__(self, model: DecoderModel, max_tokens: int, page_size: int = 64,
-                 max_slots: Optional[int] = None):
+                 max_slots: Optional[int] = None, use_graphs: bool = True):
         self.model = model
         self.rt = model.rt
         self.cache = PagedCache(model.cache_requirements(), max_tokens=max_tokens,
@@ -85,6 +85,11 @@ class Engine:
             # library products accumulate in float32 all the way, and the float32 engine never uses them
             torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
             torch.backends.cuda.matmul.allow_tf32 = False
+        # decode steps are replayed from CUDA graphs when every part allows it
+        self.graphs = None
+        if use_graphs and model.rt.device.type == "cuda" and model.graph_safe:
+            from .graphs import DecodeGraphs
+            self.graphs = DecodeGraphs(model, self.cache)
 
     # ---- slots ---------------------------------------------------------------------
     def alloc_slot(self) -> int:
@@ -130,9 +135,24 @@ class Engine:
         (toks, pos, slot, want_rows), (starts, lens, past) = self.describe(entries)
         slots = [e.slot for e in entries]
         self.cache.prepare(slots, lens)                  # raises before anything is launched
-        d_toks, d_pos, d_slot, d_want = self._staging.upload([toks, pos, slot, want_rows])
+        if self.graphs is not None and all(n == 1 for n in lens):
+            logits = self.graphs.run(slots, past, toks, None)
+            if logits is not None:
+                self.cache.commit(slots, lens)
+                if want_rows.size == 0:
+                    return None
+                if want_rows.size == len(slots):         # one token each and each wanted: rows as they are
+                    return logits
+                return logits[torch.from_numpy(want_rows.astype(np.int64)).to(logits.device)]
+        single = all(n == 1 for n in lens)
+        tiles = np.zeros((0, 4), dtype=np.int32) if single else np.asarray(
+            [(s, st + r0, min(64, n - r0), p + r0)
+             for s, st, n, p in zip(slots, starts, lens, past) for r0 in range(0, n, 64)], dtype=np.int32)
+        # the runs go first: the kernels read them 16 bytes at a time
+        d_tiles, d_toks, d_pos, d_slot, d_want = self._staging.upload([tiles.reshape(-1), toks, pos, slot, want_rows])
         ctx = StepContext(
             n_tokens=int(toks.size), tokens=d_toks, tok_pos=d_pos, tok_slot=d_slot,
+            q_tiles=None if single else d_tiles.view(-1, 4),
             seq_slots=slots, seq_starts=starts, seq_lens=lens, seq_past=past,
             all_single=all(n == 1 for n in lens),
             max_kv_len=max(p + n for p, n in zip(past, lens)),
@@ -154,6 +174,11 @@ class Engine:
         lens = [1] * n
         self.cache.prepare(slots, lens)
         past = [self.cache.length(s) for s in slots]
+        if self.graphs is not None:
+            logits = self.graphs.run(slots, past, None, tokens)
+            if logits is not None:
+                self.cache.commit(slots, lens)
+                return logits
         d_pos, d_slot, d_want = self._staging.upload([np.asarray(past, dtype=np.int32),
                                                       np.asarray(slots, dtype=np.int32),
                                                       np.arange(n, dtype=np.int32)])
@@ -163,6 +188,11 @@ class Engine:
         logits = self.model.forward(ctx, self.cache, d_want)
         self.cache.commit(slots, lens)
         return logits
+
+    @property
+    def bytes_uploaded(self) -> int:
+        """Bytes of step descriptions (ids, positions, slots) copied to the device so far."""
+        return self._staging.bytes_uploaded + (self.graphs.bytes_uploaded if self.graphs else 0)
 
     def check(self) -> None:
         """Raise if a kernel of an earlier step met an index outside the cache (synchronises)."""

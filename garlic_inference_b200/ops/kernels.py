@@ -11,7 +11,7 @@ from typing import Optional
 
 import torch
 
-from .library import KernelError, check, require_gpu
+from .library import KernelError, check, counters, require_gpu
 
 F32, BF16 = 0, 1
 _CODES = {torch.float32: F32, torch.bfloat16: BF16}
@@ -230,4 +230,64 @@ def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor], streams: O
     _dense(out, "out", torch.int32)
     check(l.gi_sample(_ptr(logits), logits.stride(0), n, vocab, _ptr(temperature), _ptr(streams), _ptr(counters),
                       int(seed) & 0xFFFFFFFFFFFFFFFF, _ptr(out), _stream()), l)
+    return out
+
+
+def mma_attention_takes(dtype: torch.dtype, head_dim: int) -> bool:
+    """Whether the tensor-core attention kernels take this element type and head size."""
+    return dtype == torch.bfloat16 and head_dim % 16 == 0 and 16 <= head_dim <= 128
+
+
+def attention_prefill_bf16(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: torch.Tensor,
+                           q_tiles: torch.Tensor, scale: float, window: int) -> torch.Tensor:
+    """Flash attention of q [n, n_q, d] over the paged cache for steps with several tokens per sequence.
+    `q_tiles` int32 [n_tiles, 4] cuts the rows into runs of at most 64 consecutive tokens of one
+    sequence: {slot, first row, rows, position of the first row}.  Returns [n, n_q * d]."""
+    l = require_gpu()
+    _dense(q, "q", torch.bfloat16), _dense(k_pool, "k_pool", torch.bfloat16), _dense(v_pool, "v_pool", torch.bfloat16)
+    _dense(block_table, "block_table", torch.int32), _dense(q_tiles, "q_tiles", torch.int32)
+    n, n_q, d = q.shape
+    n_pages, n_kv, page_size, pool_d = k_pool.shape
+    if pool_d != d or v_pool.shape != k_pool.shape:
+        raise KernelError(f"cache pools {tuple(k_pool.shape)} do not fit head_dim {d}")
+    if q_tiles.dim() != 2 or q_tiles.shape[1] != 4 or q_tiles.data_ptr() % 16:
+        raise KernelError("q_tiles must be int32 [n_tiles, 4] starting on 16 bytes")
+    out = torch.zeros((n, n_q * d), dtype=q.dtype, device=q.device)       # rows in no tile (padding) stay zero
+    check(l.gi_attention_prefill_bf16(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_table), _ptr(q_tiles),
+                                      q_tiles.shape[0], _ptr(out), n_q, n_kv, d, page_size, block_table.shape[1],
+                                      n_pages, int(window or 0), float(scale), _stream()), l)
+    return out
+
+
+def decode_splits(n_seqs: int, n_kv: int) -> int:
+    """Slices of the keys per (sequence, key/value head) in the decode kernel: enough CTAs to fill the
+    GPU a few times over at small batches, one slice once the batch alone does."""
+    return max(1, min(32, -(-1184 // max(1, n_seqs * n_kv))))
+
+
+def attention_decode_bf16(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: torch.Tensor,
+                          tok_pos: torch.Tensor, tok_slot: torch.Tensor, scale: float, window: int,
+                          n_splits: Optional[int] = None) -> torch.Tensor:
+    """Split-KV attention for decode steps: q [n_seqs, n_q, d], one token per sequence at position
+    tok_pos (the key at that position is already in the cache).  Returns [n_seqs, n_q * d].
+    The partial results of the slices go through scratch memory allocated here."""
+    l = require_gpu()
+    _dense(q, "q", torch.bfloat16), _dense(k_pool, "k_pool", torch.bfloat16), _dense(v_pool, "v_pool", torch.bfloat16)
+    for t, name in ((tok_pos, "tok_pos"), (tok_slot, "tok_slot"), (block_table, "block_table")):
+        _dense(t, name, torch.int32)
+    n, n_q, d = q.shape
+    n_pages, n_kv, page_size, pool_d = k_pool.shape
+    if pool_d != d or v_pool.shape != k_pool.shape:
+        raise KernelError(f"cache pools {tuple(k_pool.shape)} do not fit head_dim {d}")
+    if tok_pos.numel() < n or tok_slot.numel() < n:
+        raise KernelError("tok_pos / tok_slot are shorter than the token rows")
+    n_splits = n_splits or decode_splits(n, n_kv)
+    out = torch.empty((n, n_q * d), dtype=q.dtype, device=q.device)
+    part_o = torch.empty((n * n_q * n_splits * d,), dtype=torch.float32, device=q.device)
+    part_ml = torch.empty((n * n_q * n_splits * 2,), dtype=torch.float32, device=q.device)
+    check(l.gi_attention_decode_bf16(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_table), _ptr(tok_pos),
+                                     _ptr(tok_slot), _ptr(out), _ptr(part_o), _ptr(part_ml), n, n_q, n_kv, d,
+                                     page_size, block_table.shape[1], n_pages, int(window or 0), float(scale),
+                                     n_splits, _stream()), l)
+    counters.launches += 1                                   # the combine kernel
     return out

@@ -32,6 +32,8 @@ _SIGNATURES = {
     "gi_qk_norm_rope_append": ([P, P, P, P, I, P, P, I, F, P, P, I, P, P, P,
                                 I, I, I, I, I, I, I, I, I, P, P], I),
     "gi_attention_generic": ([P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, I, F, P, P], I),
+    "gi_attention_prefill_bf16": ([P, P, P, P, P, I, P, I, I, I, I, I, I, I, F, P], I),
+    "gi_attention_decode_bf16": ([P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, P], I),
     "gi_sgemm_nt": ([P, P, P, I, I, I, L, L, P], I),
     "gi_gemv_bf16": ([P, P, P, I, I, I, I, P], I),
     "gi_sample": ([P, L, I, I, P, P, P, c_ulonglong, P, P], I),

@@ -23,6 +23,7 @@ from .base import Mixer, register_part
 
 class GQAAttention(Mixer):
     kind = "gqa_attention"
+    graph_safe = True
 
     @classmethod
     def wanted(cls, params):
@@ -75,7 +76,18 @@ class GQAAttention(Mixer):
         return linear(o, self.w_o)
 
     def attend(self, q, kv, ctx):
-        """Attention of q [n, n_q, d] over the cache; returns [n, n_q * d]."""
+        """Attention of q [n, n_q, d] over the cache; returns [n, n_q * d].
+
+        bfloat16 with a head size the tensor-core kernels take: the split-KV kernel when every
+        sequence brings one token, the flash kernel when the step carries runs of tokens.  Everything
+        else (float32, other head sizes, groups beyond 16 in decode) goes to the exact-order kernel."""
+        if kernels.mma_attention_takes(q.dtype, self.d):
+            if ctx.all_single and self.n_q // self.n_kv <= 16:
+                return kernels.attention_decode_bf16(q, kv.k_pool, kv.v_pool, kv.block_table, ctx.tok_pos,
+                                                     ctx.tok_slot, self.scale, self.window or 0)
+            if not ctx.all_single and ctx.q_tiles is not None:
+                return kernels.attention_prefill_bf16(q, kv.k_pool, kv.v_pool, kv.block_table, ctx.q_tiles,
+                                                      self.scale, self.window or 0)
         return kernels.attention_generic(q, kv.k_pool, kv.v_pool, kv.block_table, ctx.tok_pos, ctx.tok_slot,
                                          self.scale, self.window or 0, ctx.status)
 

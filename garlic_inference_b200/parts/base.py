@@ -72,11 +72,21 @@ class StepContext:
     seq_past: list = field(default_factory=list)       # positions already in the cache
     all_single: bool = False            # every sequence brings exactly one token (a decode step)
     max_kv_len: int = 0                 # longest sequence after this step (an upper bound is allowed)
+    # the rows cut into runs of at most 64 consecutive tokens of one sequence, int32 [n_runs, 4] =
+    # {slot, first row, rows, position of the first row}; None in decode steps
+    q_tiles: Optional[torch.Tensor] = None
     status: Optional[torch.Tensor] = None   # int32[1] error flag shared with the cache
+    captured: bool = False              # the step is being recorded into a CUDA graph: the host-side
+                                        # lists above are empty, everything must come from the tensors
 
 
 class Part:
     kind: str = ""
+    # True if `step` reads the batch only through the context's device tensors and the cache's
+    # tensors, so that a recorded decode step can be replayed for other sequences.  A part that
+    # walks `seq_slots` / `seq_lens` on the host leaves this False and the engine launches it
+    # step by step.
+    graph_safe: bool = False
 
     @classmethod
     def wanted(cls, params: dict) -> dict[str, TensorWant]:

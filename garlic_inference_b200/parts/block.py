@@ -29,6 +29,11 @@ class PreNormResidualBlock(Block):
     def cache_requirement(self):
         return self.mixer.cache_requirement()
 
+    @property
+    def graph_safe(self):
+        return all(p.graph_safe for p in (self.mixer, self.feed_forward, self.norm_in, self.norm_post)) and \
+            (self.position is None or self.position.graph_safe)
+
     def step(self, delta, residual, ctx, cache, writes_cache=True):
         x = self.norm_in.add_norm(delta, residual)
         a = self.mixer.step(x, ctx, cache, self.position, writes_cache)
@@ -39,6 +44,7 @@ class PreNormResidualBlock(Block):
 class TokenEmbedding(Embedding):
     """h[t] = table[id[t]], no scaling (src/src-cuda/embedding.cu:29-53), written as float32."""
     kind = "token_embedding"
+    graph_safe = True
 
     @classmethod
     def wanted(cls, params):
@@ -55,6 +61,7 @@ class TokenEmbedding(Embedding):
 class LinearHead(Head):
     """logits = normed . W^T as float32 (src/models/qwen3/qwen3.cpp:302-303), on the rows asked for only."""
     kind = "linear_head"
+    graph_safe = True
 
     @classmethod
     def wanted(cls, params):

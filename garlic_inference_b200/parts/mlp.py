@@ -14,6 +14,7 @@ from .base import FeedForward, register_part
 
 class SwiGLUMLP(FeedForward):
     kind = "swiglu_mlp"
+    graph_safe = True
 
     @classmethod
     def wanted(cls, params):

@@ -10,6 +10,7 @@ from .base import Norm, register_part
 
 class RMSNorm(Norm):
     kind = "rms_norm"
+    graph_safe = True
 
     @classmethod
     def wanted(cls, params):

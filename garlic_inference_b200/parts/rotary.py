@@ -16,6 +16,7 @@ from .base import PositionEncoding, register_part
 
 class RotaryPositions(PositionEncoding):
     kind = "rotary"
+    graph_safe = True
 
     def __init__(self, params, load, rt):
         super().__init__(params, load, rt)

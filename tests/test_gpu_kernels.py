@@ -377,3 +377,102 @@ def test_temperature_draws_follow_the_softmax_and_the_key():
     temps[:10] = 0.0
     mixed = K().sample(logits, temps, streams, counters, 1234)
     assert mixed[:10].tolist() == [int(row.argmax())] * 10 and torch.equal(mixed[10:], draws[10:])
+
+
+# ------------------------------------------------------------------ tensor-core attention (bfloat16)
+def _tiles_for(runs):
+    """runs: (slot, first row, rows, first position) per sequence -> int32 [n, 4] cut at 64 rows."""
+    out = []
+    for slot, row0, n, pos0 in runs:
+        for r0 in range(0, n, 64):
+            out.append((slot, row0 + r0, min(64, n - r0), pos0 + r0))
+    return torch.tensor(out, dtype=torch.int32, device=DEV)
+
+
+@pytest.mark.parametrize("n_q,n_kv,d,page,window", [
+    (4, 4, 16, 16, 0), (5, 1, 48, 8, 0), (6, 1, 32, 16, 20), (8, 2, 128, 64, 0), (4, 2, 128, 32, 70),
+    (10, 2, 80, 64, 0), (3, 3, 112, 16, 0), (2, 1, 64, 128, 130)])
+def test_attention_prefill_bf16(n_q, n_kv, d, page, window):
+    lens = [1, 37, 200, 64, 65, 130]
+    new = [1, 37, 150, 64, 3, 129]           # the last `new` positions of each sequence are this step's queries
+    k_pool, v_pool, bt, kd, vd = make_cache(len(lens), lens, n_kv, d, page, torch.bfloat16, seed=d + n_q)
+    runs, row = [], 0
+    for s, (n, m) in enumerate(zip(lens, new)):
+        runs.append((s, row, m, n - m))
+        row += m
+    row += 2                                   # two padding rows at the end, in no tile
+    g = torch.Generator(device=DEV).manual_seed(17)
+    q = torch.randn(row, n_q, d, generator=g, device=DEV).to(torch.bfloat16)
+    scale = d ** -0.5
+    out = K().attention_prefill_bf16(q, k_pool, v_pool, bt, _tiles_for(runs), scale, window).float().view(row, n_q, d)
+    assert float(out[-2:].abs().sum()) == 0
+    for s, row0, m, pos0 in runs:
+        for i in range(m):
+            ref = ref_attention(q[row0 + i].float(), kd[s], vd[s], pos0 + i, scale, window).float()
+            torch.testing.assert_close(out[row0 + i], ref, rtol=2e-2, atol=2e-2,
+                                       msg=lambda msg: f"seq {s} position {pos0 + i}: {msg}")
+
+
+@pytest.mark.parametrize("n_q,n_kv,d,page,window,splits", [
+    (4, 4, 16, 16, 0, None), (5, 1, 48, 8, 0, 3), (6, 1, 32, 16, 20, None), (32, 8, 128, 64, 0, None),
+    (8, 2, 128, 32, 70, 1), (16, 1, 80, 64, 0, 32), (3, 3, 112, 16, 0, 7), (10, 2, 64, 128, 130, 2)])
+def test_attention_decode_bf16(n_q, n_kv, d, page, window, splits):
+    lens = [1, 37, 700, 64, 65, 130, 63]
+    k_pool, v_pool, bt, kd, vd = make_cache(len(lens), lens, n_kv, d, page, torch.bfloat16, seed=d + n_q + 1)
+    slots = [0, 1, 2, 3, -1, 4, 5, 6]                                   # one padding row in the middle
+    pos = [lens[s] - 1 if s >= 0 else 0 for s in slots]
+    g = torch.Generator(device=DEV).manual_seed(18)
+    q = torch.randn(len(slots), n_q, d, generator=g, device=DEV).to(torch.bfloat16)
+    scale = d ** -0.5
+    out = K().attention_decode_bf16(q, k_pool, v_pool, bt, torch.tensor(pos, dtype=torch.int32, device=DEV),
+                                    torch.tensor(slots, dtype=torch.int32, device=DEV), scale, window,
+                                    n_splits=splits).float().view(len(slots), n_q, d)
+    for i, s in enumerate(slots):
+        if s < 0:
+            assert float(out[i].abs().sum()) == 0, "a padding row gives zeros"
+            continue
+        ref = ref_attention(q[i].float(), kd[s], vd[s], pos[i], scale, window).float()
+        torch.testing.assert_close(out[i], ref, rtol=2e-2, atol=2e-2, msg=lambda msg: f"seq {s}: {msg}")
+
+
+@pytest.mark.parametrize("kernel", ["decode", "prefill"])
+def test_tensor_core_attention_finds_one_far_key(kernel):
+    n_q, n_kv, d, page, n = 8, 2, 64, 16, 700
+    for far in (0, 1, 15, 16, 63, 64, 333, 639, 640, 698, 699):
+        k_pool, v_pool, bt, kd, vd = make_cache(1, [n], n_kv, d, page, torch.bfloat16, seed=far + 1)
+        q = torch.zeros(1, n_q, d, device=DEV)
+        for h in range(n_q):
+            q[0, h] = kd[0][far, h // 4] * 4.0
+        q = q.to(torch.bfloat16)
+        pos = torch.tensor([n - 1], dtype=torch.int32, device=DEV)
+        z = torch.zeros(1, dtype=torch.int32, device=DEV)
+
+        def run(window):
+            if kernel == "decode":
+                return K().attention_decode_bf16(q, k_pool, v_pool, bt, pos, z, 1.0, window).float().view(n_q, d)
+            return K().attention_prefill_bf16(q, k_pool, v_pool, bt, _tiles_for([(0, 0, 1, n - 1)]), 1.0,
+                                              window).float().view(n_q, d)
+
+        out = run(0)
+        for h in range(n_q):
+            torch.testing.assert_close(out[h], vd[0][far, h // 4], rtol=2e-2, atol=2e-2,
+                                       msg=lambda msg: f"{kernel}: far key {far}, head {h}: {msg}")
+        if far < n - 40:
+            assert float((run(n - 1 - far)[0] - vd[0][far, 0]).abs().max()) > 0.1, "the window's edge lets it in"
+            torch.testing.assert_close(run(n - far)[0], vd[0][far, 0], rtol=2e-2, atol=2e-2)
+
+
+def test_tensor_core_attention_refuses_other_sizes():
+    from garlic_inference_b200.ops import KernelError
+    q = torch.zeros(1, 34, 64, dtype=torch.bfloat16, device=DEV)
+    pool = torch.zeros(2, 2, 16, 64, dtype=torch.bfloat16, device=DEV)
+    bt = torch.zeros(1, 2, dtype=torch.int32, device=DEV)
+    z = torch.zeros(1, dtype=torch.int32, device=DEV)
+    with pytest.raises(KernelError, match="up to 16"):
+        K().attention_decode_bf16(q, pool, pool, bt, z, z, 1.0, 0)
+    q2 = torch.zeros(1, 2, 256, dtype=torch.bfloat16, device=DEV)
+    pool2 = torch.zeros(2, 2, 16, 256, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(KernelError, match="multiple of 16 up to 128"):
+        K().attention_decode_bf16(q2, pool2, pool2, bt, z, z, 1.0, 0)
+    assert not K().mma_attention_takes(torch.bfloat16, 256) and not K().mma_attention_takes(torch.float32, 64)
+    assert K().mma_attention_takes(torch.bfloat16, 48)

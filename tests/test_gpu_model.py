@@ -138,6 +138,29 @@ def test_padding_rows_change_nothing(gpu_models, plain_cache):
     eng.check()
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_recorded_decode_steps_equal_launched_ones(dtype, model_dirs, plain_cache):
+    """Decode steps replayed from CUDA graphs (the default) against the same steps launched kernel by
+    kernel: same bits in float32; batches of 1, 2, 3 (padded to 4) and 5 (padded to 8) sequences."""
+    from garlic_inference_b200 import AutoModel
+    reqs, want = plain_cache("C")
+    steps = tiny.trace_batched(reqs, [["r0"], ["r1", "r2"], ["r3", "r4", "r5"], ["r0", "r1", "r2", "r3", "r6"]],
+                               prompt_frac=0.3)
+    got = {}
+    for graphs in (True, False):
+        model = AutoModel.from_pretrained(model_dirs("C"), device=0, dtype=dtype, max_tokens=1024, page_size=16,
+                                          use_graphs=graphs)
+        assert (model.engine.graphs is not None) == graphs
+        got[graphs] = tiny.run_trace_in_process(model, steps)
+        tiny.compare(got[graphs], want, tiny.TOL[dtype], f"C {dtype} graphs={graphs}")
+        if graphs:
+            assert sorted(model.engine.graphs._graphs) == [1, 2, 4, 8]
+    if dtype == "float32":
+        for rid in got[True]:
+            for p in got[True][rid]:
+                assert np.array_equal(got[True][rid][p], got[False][rid][p]), f"{rid} position {p}"
+
+
 def test_step_errors_come_before_any_launch(gpu_models):
     from garlic_inference_b200.cache import CacheError
     from garlic_inference_b200.engine import StepEntry, StepError

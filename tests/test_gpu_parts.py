@@ -105,7 +105,10 @@ def _attention_setup(dtype, window, n_q=6, n_kv=2, d=32, hidden=96, S=50, page=1
                            tok_pos=torch.arange(lo, hi, dtype=torch.int32, device=DEV),
                            tok_slot=torch.full((n,), slot, dtype=torch.int32, device=DEV),
                            seq_slots=[slot], seq_starts=[0], seq_lens=[n], seq_past=[lo], all_single=(n == 1),
-                           max_kv_len=hi, status=cache.status)
+                           max_kv_len=hi, status=cache.status,
+                           q_tiles=None if n == 1 else torch.tensor(
+                               [(slot, r0, min(64, n - r0), lo + r0) for r0 in range(0, n, 64)],
+                               dtype=torch.int32, device=DEV))
     return part, rope, cache, x.to(DEV), want, ctx_for
 
 
