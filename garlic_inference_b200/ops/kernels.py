@@ -206,6 +206,21 @@ def gemv_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch
     return out
 
 
+def gemm_skinny_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, n_split: int = 0,
+                     wide: int = -1) -> torch.Tensor:
+    """x [M<=16, K] . w[N,K]^T on the tensor cores with W streamed once.  K is shared by a cluster of
+    `n_split` CTAs (1 to 8; 0: chosen from the sizes); `wide` picks 64 (1) or 32 (0) rows of W per
+    CTA (-1: chosen from the sizes)."""
+    l = require_gpu()
+    _dense(x, "x", torch.bfloat16), _dense(w, "w", torch.bfloat16)
+    (m, k), (n, k2) = x.shape, w.shape
+    if k != k2:
+        raise KernelError(f"inner sizes differ: x {tuple(x.shape)}, w {tuple(w.shape)}")
+    out = torch.empty((m, n), dtype=out_dtype, device=x.device)
+    check(l.gi_gemm_skinny_bf16(_ptr(x), _ptr(w), _ptr(out), code(out_dtype), m, n, k, n_split, wide, _stream()), l)
+    return out
+
+
 def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor], streams: Optional[torch.Tensor],
            counters: Optional[torch.Tensor], seed: int, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """One token per row of float32 logits [n, vocab]: greedy where temperature <= 0 (or None),

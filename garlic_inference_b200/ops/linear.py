@@ -4,7 +4,9 @@ Which product runs:
   * float32 weight: this package's own float32 FMA kernel (no tensor-core or
     reduced-precision mode); bfloat16 activations are widened first and the
     result narrowed again.
-  * bfloat16 weight, up to 8 rows: this package's bandwidth kernel.
+  * bfloat16 weight, one row: this package's bandwidth kernel (GEMV).
+  * bfloat16 weight, 2 to 8 rows: this package's tensor-core kernel for
+    decode batches, which reads the weight once.
   * bfloat16 weight, more rows: the library product (cuBLAS through
     `torch.mm`), float32 accumulation.  Upstream uses the same library for all
     its products (src/src-cuda/mat-ops/gemm/gemm.cu:22-41).
@@ -18,7 +20,8 @@ import torch
 from . import kernels
 from .library import KernelError
 
-GEMV_MAX_ROWS = 8
+GEMV_MAX_ROWS = 1          # one row: the plain bandwidth kernel
+SKINNY_MAX_ROWS = 8        # up to here: the tensor-core kernel that streams W once (it takes 16; the library is faster from 9 on)
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
@@ -35,8 +38,10 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
     m, k = x.shape
     if m == 0:
         return torch.empty((0, w.shape[0]), dtype=out_dtype, device=x.device)
-    if m <= GEMV_MAX_ROWS and k % 8 == 0 and w.data_ptr() % 16 == 0 and x.data_ptr() % 16 == 0:
-        return kernels.gemv_bf16(x, w, out_dtype)
+    if m <= SKINNY_MAX_ROWS and k % 8 == 0 and w.data_ptr() % 16 == 0 and x.data_ptr() % 16 == 0:
+        if m <= GEMV_MAX_ROWS:
+            return kernels.gemv_bf16(x, w, out_dtype)
+        return kernels.gemm_skinny_bf16(x, w, out_dtype)
     kernels.require_gpu()
     if out_dtype == torch.float32:
         return torch.mm(x, w.t(), out_dtype=torch.float32)

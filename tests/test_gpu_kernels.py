@@ -132,6 +132,22 @@ def test_gemv_bf16(m, out_dtype):
         torch.testing.assert_close(out.float(), ref.to(torch.bfloat16).float(), **ulp_tol(torch.bfloat16))
 
 
+@pytest.mark.parametrize("m", [1, 2, 5, 8, 9, 16])
+@pytest.mark.parametrize("n,k,split,wide", [(1003, 264, 0, -1), (4096, 4096, 0, -1), (96, 1288, 8, 0), (130, 12288, 3, 1),
+                                           (6144, 520, 2, 1), (50, 64, 1, 0), (40, 8, 0, -1), (200, 2048, 6, 0),
+                                           (15000, 128, 0, -1)])
+def test_gemm_skinny_bf16(m, n, k, split, wide):
+    g = torch.Generator(device=DEV).manual_seed(m * 1000 + n)
+    x = torch.randn(m, k, generator=g, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(n, k, generator=g, device=DEV) * 0.1).to(torch.bfloat16)
+    ref = x.float() @ w.float().T
+    out32 = K().gemm_skinny_bf16(x, w, torch.float32, n_split=split, wide=wide)
+    torch.testing.assert_close(out32, ref, rtol=1e-4, atol=2e-4 * math.sqrt(k))
+    out16 = K().gemm_skinny_bf16(x, w, torch.bfloat16, n_split=split, wide=wide)
+    torch.testing.assert_close(out16.float(), ref.to(torch.bfloat16).float(), **ulp_tol(torch.bfloat16))
+    assert torch.equal(out32, K().gemm_skinny_bf16(x, w, torch.float32, n_split=split, wide=wide)), "same bits from run to run"
+
+
 def test_kernels_refuse_what_they_cannot_take():
     from garlic_inference_b200.ops import KernelError
     x = torch.zeros(9, 64, dtype=torch.bfloat16, device=DEV)
