@@ -46,6 +46,7 @@ attn_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, const
                     const int* __restrict__ tok_slot, T* __restrict__ out, int n_q, int n_kv, int d,
                     int page_size, int max_pages, int n_pool_pages, int window, float scale,
                     int* __restrict__ status) {
+    gi_pdl_start();
     extern __shared__ float smem[];
     float* q_s = smem;                       // d
     float* acc_s = smem + d;                 // AG_WARPS * d
@@ -141,7 +142,7 @@ static int launch_generic(const void* q, const void* k_pool, const void* v_pool,
     dim3 grid(n_tokens, n_q);
     const size_t smem = ((size_t)d * (1 + AG_WARPS) + 2 * AG_WARPS) * sizeof(float);
 #define AG_LAUNCH(DPL)                                                                               \
-    attn_generic_kernel<T, DPL><<<grid, AG_WARPS * 32, smem, s>>>(                                    \
+    gi_launch(attn_generic_kernel<T, DPL>, grid, dim3(AG_WARPS * 32), smem, s,                                     \
         (const T*)q, (const T*)k_pool, (const T*)v_pool, block_table, tok_pos, tok_slot, (T*)out,     \
         n_q, n_kv, d, page_size, max_pages, n_pool_pages, window, scale, status)
     if (d <= 32) AG_LAUNCH(1);

@@ -18,7 +18,8 @@
 //   decode:  one CTA = one sequence, one key/value head, one slice of the
 //            keys; the rows of the product are the n_q / n_kv query heads of
 //            the group (at most 16); the 4 warps take 16 keys each of every
-//            tile and are merged at the end.  Each slice writes a partial
+//            tile, each streaming them through a queue of its own, and are
+//            merged at the end.  Each slice writes a partial
 //            (max, sum, unnormalised output) to scratch memory; the combine
 //            kernel merges the slices.  The number of slices is a launch
 //            parameter; which keys a slice covers follows from the sequence's
@@ -31,6 +32,7 @@
 #define AT_THREADS 128
 #define AT_BN 64            // keys per tile
 #define AT_BM 64            // queries per prefill CTA
+#define AT_DEC_DEPTH 2      // stages of a warp's queue in the decode kernel
 
 // ------------------------------------------------------------------------------ PTX helpers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -60,6 +62,18 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// Element offset of row j of a sequence inside a pool (for key/value head kvh), or -1 when j is not below
+// key_end or its page is not mapped.  No branch around the table read, so that a thread's reads for
+// several rows are issued together instead of one after the other.
+__device__ __forceinline__ long long kv_row_offset(const int* __restrict__ bt_row, int j, int key_end, int n_kv, int kvh,
+                                                   int page_size, int max_pages, int n_pool_pages, int D) {
+    const int lp = j / page_size;
+    const bool in = j >= 0 && j < key_end && lp < max_pages;
+    const int page = __ldg(bt_row + (in ? lp : 0));
+    const bool ok = in && page >= 0 && page < n_pool_pages;
+    return ok ? (((long long)page * n_kv + kvh) * page_size + (j - lp * page_size)) * D : -1;
+}
+
 // Stage one tile of 64 keys (rows key0 .. key0+63 of the sequence) of keys and values into shared memory.
 // Rows at or beyond key_end, and rows whose page is not mapped, are zero-filled.
 template <int D>
@@ -67,22 +81,20 @@ __device__ __forceinline__ void load_kv_tile(bf16* sK, bf16* sV, const bf16* __r
                                              const bf16* __restrict__ v_pool, const int* __restrict__ bt_row,
                                              int key0, int key_end, int n_kv, int kvh, int page_size,
                                              int max_pages, int n_pool_pages) {
-    constexpr int LD = D + 8, CH = D / 8;
+    constexpr int LD = D + 8, CH = D / 8, PASSES = AT_BN * CH / AT_THREADS;
+    long long off[PASSES];
 #pragma unroll
-    for (int p = 0; p < AT_BN * CH / AT_THREADS; ++p) {
+    for (int p = 0; p < PASSES; ++p)
+        off[p] = kv_row_offset(bt_row, key0 + (threadIdx.x + p * AT_THREADS) / CH, key_end, n_kv, kvh, page_size,
+                               max_pages, n_pool_pages, D);
+#pragma unroll
+    for (int p = 0; p < PASSES; ++p) {
         const int i = threadIdx.x + p * AT_THREADS;
         const int r = i / CH, c = i % CH;
-        const int j = key0 + r;
-        bool valid = j >= 0 && j < key_end;
-        size_t off = 0;
-        if (valid) {
-            const int lp = j / page_size;
-            const int page = lp < max_pages ? bt_row[lp] : -1;
-            valid = page >= 0 && page < n_pool_pages;
-            if (valid) off = (((size_t)page * n_kv + kvh) * page_size + (j - lp * page_size)) * D + c * 8;
-        }
-        cp_async_16(sK + r * LD + c * 8, k_pool + off, valid);
-        cp_async_16(sV + r * LD + c * 8, v_pool + off, valid);
+        const bool valid = off[p] >= 0;
+        const size_t o = valid ? (size_t)off[p] + c * 8 : 0;
+        cp_async_16(sK + r * LD + c * 8, k_pool + o, valid);
+        cp_async_16(sV + r * LD + c * 8, v_pool + o, valid);
     }
 }
 
@@ -181,6 +193,7 @@ __global__ void __launch_bounds__(AT_THREADS)
 flash_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool,
                      const int* __restrict__ block_table, const int4* __restrict__ tiles, bf16* __restrict__ out,
                      int n_q, int n_kv, int page_size, int max_pages, int n_pool_pages, int window, float scale_log2) {
+    gi_pdl_start();
     constexpr int LD = D + 8;
     extern __shared__ __align__(16) unsigned char at_smem[];
     bf16* sQ = reinterpret_cast<bf16*>(at_smem);
@@ -282,11 +295,12 @@ decode_splitkv_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_poo
                       const int* __restrict__ tok_slot, float* __restrict__ part_o, float* __restrict__ part_ml,
                       int n_q, int n_kv, int page_size, int max_pages, int n_pool_pages, int window,
                       float scale_log2, int n_splits) {
-    constexpr int LD = D + 8;
+    gi_pdl_start();
+    constexpr int LD = D + 8, CH = D / 8;
+    constexpr int STAGE = 2 * 16 * LD;                           // elements of one warp's stage: 16 keys, 16 values
     extern __shared__ __align__(16) unsigned char at_smem[];
     bf16* sQ = reinterpret_cast<bf16*>(at_smem);                // 16 rows
-    bf16* sK = sQ + 16 * LD;
-    bf16* sV = sK + 2 * AT_BN * LD;
+    bf16* sKV = sQ + 16 * LD;                                    // [4 warps][AT_DEC_DEPTH][keys | values][16][LD]
 
     const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
     const int grp = n_q / n_kv;
@@ -314,8 +328,34 @@ decode_splitkv_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_poo
         if (r < grp) v = *reinterpret_cast<const uint4*>(q + ((size_t)b * n_q + kvh * grp + r) * D + c * 8);
         *reinterpret_cast<uint4*>(sQ + r * LD + c * 8) = v;
     }
-    load_kv_tile<D>(sK, sV, k_pool, v_pool, bt_row, lo_al + t0 * AT_BN, kv_len, n_kv, kvh, page_size, max_pages, n_pool_pages);
-    cp_async_commit();
+
+    // Each warp streams its own 16 keys (and values) of every 64-key tile through a queue of its own,
+    // AT_DEC_DEPTH stages deep: the warps never wait for each other while the cache is read.
+    bf16* ring = sKV + warp * AT_DEC_DEPTH * STAGE;
+    const int n_it = t1 - t0;
+    auto issue = [&](int i) {
+        if (i < n_it) {
+            bf16* st = ring + (i % AT_DEC_DEPTH) * STAGE;
+            const int key0 = lo_al + (t0 + i) * AT_BN + warp * 16;
+            long long off[16 * CH / 32];
+#pragma unroll
+            for (int p = 0; p < 16 * CH / 32; ++p)
+                off[p] = kv_row_offset(bt_row, key0 + (lane + p * 32) / CH, kv_len, n_kv, kvh, page_size, max_pages,
+                                       n_pool_pages, D);
+#pragma unroll
+            for (int p = 0; p < 16 * CH / 32; ++p) {
+                const int idx = lane + p * 32;
+                const int r = idx / CH, c = idx % CH;
+                const bool valid = off[p] >= 0;
+                const size_t o = valid ? (size_t)off[p] + c * 8 : 0;
+                cp_async_16(st + r * LD + c * 8, k_pool + o, valid);
+                cp_async_16(st + 16 * LD + r * LD + c * 8, v_pool + o, valid);
+            }
+        }
+        cp_async_commit();                                       // an empty group when nothing is left: the count stays uniform
+    };
+#pragma unroll
+    for (int i = 0; i < AT_DEC_DEPTH - 1; ++i) issue(i);
 
     uint32_t a[D / 16][4];
     float o[D / 8][4];
@@ -324,23 +364,18 @@ decode_splitkv_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_poo
 #pragma unroll
         for (int e = 0; e < 4; ++e) o[dt][e] = 0.f;
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    __syncthreads();                                             // the queries are in shared memory
+    load_a_frags<D>(a, sQ);
 
-    for (int it = t0; it < t1; ++it) {
-        const int st = (it - t0) & 1;
-        if (it + 1 < t1) {
-            load_kv_tile<D>(sK + (st ^ 1) * AT_BN * LD, sV + (st ^ 1) * AT_BN * LD, k_pool, v_pool, bt_row,
-                            lo_al + (it + 1) * AT_BN, kv_len, n_kv, kvh, page_size, max_pages, n_pool_pages);
-            cp_async_commit();
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
-        }
-        __syncthreads();
-        if (it == t0) load_a_frags<D>(a, sQ);
-        const int key0 = lo_al + it * AT_BN + warp * 16;              // this warp's 16 keys of the tile
+    for (int i = 0; i < n_it; ++i) {
+        issue(i + AT_DEC_DEPTH - 1);
+        cp_async_wait<AT_DEC_DEPTH - 1>();
+        __syncwarp();                                            // every lane's copies of stage i have landed
+        const bf16* st = ring + (i % AT_DEC_DEPTH) * STAGE;
+        const int key0 = lo_al + (t0 + i) * AT_BN + warp * 16;  // this warp's 16 keys of the tile
         if (key0 <= pos && key0 + 15 >= lo) {
             float s[2][4];
-            qk_product<D, 2>(s, a, sK + st * AT_BN * LD, warp * 16);
+            qk_product<D, 2>(s, a, st, 0);
 #pragma unroll
             for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
@@ -350,17 +385,19 @@ decode_splitkv_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_poo
                 }
             uint32_t pf[1][4];
             softmax_update<D, 2>(s, m, l, o, pf);
-            pv_product<D, 1>(o, pf, sV + st * AT_BN * LD, warp * 16);
+            pv_product<D, 1>(o, pf, st + 16 * LD, 0);
         }
-        __syncthreads();
+        __syncwarp();                                            // the stage may be overwritten by the next issue
     }
+    cp_async_wait<0>();
 #pragma unroll
     for (int hh = 0; hh < 2; ++hh) {
         l[hh] += __shfl_xor_sync(0xffffffffu, l[hh], 1);
         l[hh] += __shfl_xor_sync(0xffffffffu, l[hh], 2);
     }
+    __syncthreads();                                             // all warps are done with their queues
     // merge the four warps (each saw other keys) through shared memory, reusing the tile buffers
-    float* mO = reinterpret_cast<float*>(sK);                    // [4][16][D]
+    float* mO = reinterpret_cast<float*>(sKV);                   // [4][16][D]
     float* mM = mO + 4 * 16 * D;                                 // [4][16]
     float* mL = mM + 4 * 16;                                     // [4][16]
 #pragma unroll
@@ -400,6 +437,7 @@ template <int D>
 __global__ void __launch_bounds__(128)
 decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, bf16* __restrict__ out,
                       int n_splits) {
+    gi_pdl_start();
     const size_t row = blockIdx.x;                               // sequence * n_q + head
     const float* ml = part_ml + row * n_splits * 2;
     float M = -INFINITY;
@@ -465,7 +503,7 @@ extern "C" int gi_attention_prefill_bf16(const void* q, const void* k_pool, cons
     {                                                                                                          \
         const size_t smem = (size_t)(AT_BM + 4 * AT_BN) * (DD + 8) * sizeof(bf16);                             \
         if (int rc = set_smem<DD, 0>((const void*)flash_prefill_kernel<DD>, smem)) return rc;                     \
-        flash_prefill_kernel<DD><<<grid, AT_THREADS, smem, (cudaStream_t)stream>>>(                            \
+        gi_launch(flash_prefill_kernel<DD>, grid, dim3(AT_THREADS), smem, (cudaStream_t)stream,                             \
             (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, block_table, (const int4*)tiles,         \
             (bf16*)out, n_q, n_kv, page_size, max_pages, n_pool_pages, window, scale_log2);                    \
     }
@@ -489,14 +527,14 @@ extern "C" int gi_attention_decode_bf16(const void* q, const void* k_pool, const
     dim3 grid(n_splits, n_kv, n_seqs);
 #define CALL(DD)                                                                                               \
     {                                                                                                          \
-        size_t smem = (size_t)(16 + 4 * AT_BN) * (DD + 8) * sizeof(bf16);                                      \
+        size_t smem = (size_t)(16 + 4 * AT_DEC_DEPTH * 32) * (DD + 8) * sizeof(bf16);                          \
         const size_t merge = (size_t)16 * (DD + 8) * sizeof(bf16) + (size_t)(4 * 16 * DD + 128) * sizeof(float); \
         if (merge > smem) smem = merge;                                                                        \
         if (int rc = set_smem<DD, 1>((const void*)decode_splitkv_kernel<DD>, smem)) return rc;                    \
-        decode_splitkv_kernel<DD><<<grid, AT_THREADS, smem, (cudaStream_t)stream>>>(                           \
+        gi_launch(decode_splitkv_kernel<DD>, grid, dim3(AT_THREADS), smem, (cudaStream_t)stream,                            \
             (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, block_table, tok_pos, tok_slot, part_o,  \
             part_ml, n_q, n_kv, page_size, max_pages, n_pool_pages, window, scale_log2, n_splits);             \
-        decode_combine_kernel<DD><<<n_seqs * n_q, DD < 128 ? (DD < 32 ? 32 : DD) : 128, 0, (cudaStream_t)stream>>>( \
+        gi_launch(decode_combine_kernel<DD>, dim3(n_seqs * n_q), dim3(DD < 128 ? (DD < 32 ? 32 : DD) : 128), 0, (cudaStream_t)stream,  \
             part_o, part_ml, (bf16*)out, n_splits);                                                            \
     }
     AT_DISPATCH_D(d, CALL)

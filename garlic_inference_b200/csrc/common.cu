@@ -24,6 +24,17 @@ int gi_check_launch(const char* what) {
 
 extern "C" const char* gi_last_error(void) { return g_error; }
 
+#include <stdlib.h>
+#include <string.h>
+bool gi_pdl_enabled() {
+    static int enabled = -1;
+    if (enabled < 0) {
+        const char* v = getenv("GARLIC_B200_PDL");
+        enabled = (v && strcmp(v, "1") == 0) ? 1 : 0;
+    }
+    return enabled == 1;
+}
+
 // Compute capability of the current device as major*10+minor, or a negative CUDA error.
 extern "C" int gi_device_arch(void) {
     int dev = 0, major = 0, minor = 0;

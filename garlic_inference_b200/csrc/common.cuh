@@ -37,6 +37,36 @@ int gi_check_launch(const char* what);
 
 typedef __nv_bfloat16 bf16;
 
+// Programmatic dependent launch.  Every kernel of this library starts with gi_pdl_start(): when the
+// launches carry the attribute below, it lets the next kernel of the stream be launched while this one
+// still runs (its blocks then sit in their own gi_pdl_start until this grid has finished and its writes
+// are visible).  Nothing may be read or written before it.  Without the attribute both instructions do
+// nothing.  Measured on a B200 inside the recorded decode step it did not pay (batch 1: 4.6 ms a step
+// with it, 3.9 ms without), so it is off unless GARLIC_B200_PDL=1 is set in the environment.
+__device__ __forceinline__ void gi_pdl_start() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+// kernel<<<grid, block, smem, stream>>>(args...), with the attribute that allows the overlap above when
+// GARLIC_B200_PDL=1.
+bool gi_pdl_enabled();
+template <typename... KArgs, typename... Args>
+static inline void gi_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                             Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = gi_pdl_enabled() ? 1 : 0;
+    cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);      // errors surface in gi_check_launch
+}
+
 __device__ __forceinline__ float to_f32(float v) { return v; }
 __device__ __forceinline__ float to_f32(bf16 v) { return __bfloat162float(v); }
 

@@ -16,6 +16,7 @@
 __global__ void __launch_bounds__(256)
 sgemm_nt_kernel(const float* __restrict__ A, const float* __restrict__ W, float* __restrict__ C,
                 int M, int N, int K, long long lda, long long ldc) {
+    gi_pdl_start();
     __shared__ float As[SG_BK][SG_BM + 4];
     __shared__ float Ws[SG_BK][SG_BN + 4];
     const int tid = threadIdx.x;
@@ -71,6 +72,6 @@ extern "C" int gi_sgemm_nt(const float* A, const float* W, float* C, int M, int 
     const long long gy = (M + SG_BM - 1) / SG_BM;
     GI_REQUIRE(gy <= 65535, "gi_sgemm_nt: %d rows in one product is beyond %d", M, 65535 * SG_BM);
     dim3 grid((N + SG_BN - 1) / SG_BN, (unsigned)gy);
-    sgemm_nt_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(A, W, C, M, N, K, lda, ldc);
+    gi_launch(sgemm_nt_kernel, grid, dim3(256), 0, (cudaStream_t)stream, A, W, C, M, N, K, lda, ldc);
     return gi_check_launch("gi_sgemm_nt");
 }

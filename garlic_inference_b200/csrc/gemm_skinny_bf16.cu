@@ -65,6 +65,7 @@ __global__ void __launch_bounds__(SK_THREADS)
 skinny_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, void* __restrict__ out, int out_f32,
                    int M, int N, int K, int k_slice) {
     static_assert(WR * WK == SK_WARPS, "8 warps");
+    gi_pdl_start();
     constexpr int MP = 8 * NT;                   // padded batch
     constexpr int R = 16 * WR;                   // W rows per CTA
     constexpr int CH = 4;                        // 16-byte pieces of W a thread brings in per chunk
@@ -195,13 +196,15 @@ static int launch_skinny(const bf16* x, const bf16* W, void* out, int out_f32, i
     cfg.blockDim = dim3(SK_THREADS, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 1;
     attr[0].val.clusterDim.y = n_split;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = gi_pdl_enabled() ? 2 : 1;
     cudaError_t e = cudaLaunchKernelEx(&cfg, skinny_gemm_kernel<NT, WR, WK>, x, W, out, out_f32, M, N, K, k_slice);
     if (e != cudaSuccess) { gi_set_error("gi_gemm_skinny_bf16: launch: %s", cudaGetErrorString(e)); return (int)e; }
     return gi_check_launch("gi_gemm_skinny_bf16");

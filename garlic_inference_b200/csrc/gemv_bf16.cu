@@ -38,6 +38,7 @@ __device__ __forceinline__ void fma8(const uint4& w, const bf16* __restrict__ x,
 template <int M, typename OutT>
 __global__ void __launch_bounds__(GV_WARPS * 32)
 gemv_bf16_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, OutT* __restrict__ out, int N, int K) {
+    gi_pdl_start();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n = blockIdx.x * GV_WARPS + warp;
     if (n >= N) return;
@@ -70,14 +71,14 @@ template <typename OutT>
 static int launch_gemv(const bf16* x, const bf16* W, OutT* out, int M, int N, int K, cudaStream_t s) {
     const int blocks = (N + GV_WARPS - 1) / GV_WARPS;
     switch (M) {
-        case 1: gemv_bf16_kernel<1, OutT><<<blocks, GV_WARPS * 32, 0, s>>>(x, W, out, N, K); break;
-        case 2: gemv_bf16_kernel<2, OutT><<<blocks, GV_WARPS * 32, 0, s>>>(x, W, out, N, K); break;
-        case 3: gemv_bf16_kernel<3, OutT><<<blocks, GV_WARPS * 32, 0, s>>>(x, W, out, N, K); break;
-        case 4: gemv_bf16_kernel<4, OutT><<<blocks, GV_WARPS * 32, 0, s>>>(x, W, out, N, K); break;
-        case 5: gemv_bf16_kernel<5, OutT><<<blocks, GV_WARPS * 32, 0, s>>>(x, W, out, N, K); break;
-        case 6: gemv_bf16_kernel<6, OutT><<<blocks, GV_WARPS * 32, 0, s>>>(x, W, out, N, K); break;
-        case 7: gemv_bf16_kernel<7, OutT><<<blocks, GV_WARPS * 32, 0, s>>>(x, W, out, N, K); break;
-        case 8: gemv_bf16_kernel<8, OutT><<<blocks, GV_WARPS * 32, 0, s>>>(x, W, out, N, K); break;
+        case 1: gi_launch(gemv_bf16_kernel<1, OutT>, dim3(blocks), dim3(GV_WARPS * 32), 0, s, x, W, out, N, K); break;
+        case 2: gi_launch(gemv_bf16_kernel<2, OutT>, dim3(blocks), dim3(GV_WARPS * 32), 0, s, x, W, out, N, K); break;
+        case 3: gi_launch(gemv_bf16_kernel<3, OutT>, dim3(blocks), dim3(GV_WARPS * 32), 0, s, x, W, out, N, K); break;
+        case 4: gi_launch(gemv_bf16_kernel<4, OutT>, dim3(blocks), dim3(GV_WARPS * 32), 0, s, x, W, out, N, K); break;
+        case 5: gi_launch(gemv_bf16_kernel<5, OutT>, dim3(blocks), dim3(GV_WARPS * 32), 0, s, x, W, out, N, K); break;
+        case 6: gi_launch(gemv_bf16_kernel<6, OutT>, dim3(blocks), dim3(GV_WARPS * 32), 0, s, x, W, out, N, K); break;
+        case 7: gi_launch(gemv_bf16_kernel<7, OutT>, dim3(blocks), dim3(GV_WARPS * 32), 0, s, x, W, out, N, K); break;
+        case 8: gi_launch(gemv_bf16_kernel<8, OutT>, dim3(blocks), dim3(GV_WARPS * 32), 0, s, x, W, out, N, K); break;
         default: GI_REQUIRE(false, "gi_gemv_bf16: %d rows; this kernel takes 1 to 8", M);
     }
     return gi_check_launch("gi_gemv_bf16");

@@ -28,6 +28,7 @@ __global__ void qk_norm_rope_append_kernel(
     const int* __restrict__ tok_pos, const int* __restrict__ tok_slot, const int* __restrict__ block_table,
     int n_tokens, int n_q, int n_kv, int d, int page_size, int max_pages, int n_pool_pages,
     int max_positions, int append, int* __restrict__ status) {
+    gi_pdl_start();
     extern __shared__ float head_buf[];            // ROPE_WARPS * d floats
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int heads_here = append ? n_q + 2 * n_kv : n_q;
@@ -115,7 +116,7 @@ extern "C" int gi_qk_norm_rope_append(
     const size_t smem = (size_t)ROPE_WARPS * d * sizeof(float);
     cudaStream_t s = (cudaStream_t)stream;
 #define LAUNCH(T)                                                                                     \
-    qk_norm_rope_append_kernel<T><<<(int)blocks, ROPE_WARPS * 32, smem, s>>>(                         \
+    gi_launch(qk_norm_rope_append_kernel<T>, dim3((int)blocks), dim3(ROPE_WARPS * 32), smem, s,                          \
         (const T*)qkv, (T*)q_out, (T*)k_pool, (T*)v_pool, q_w, k_w, w_dtype, eps, cos_t, sin_t,       \
         rotary_dim, tok_pos, tok_slot, block_table, n_tokens, n_q, n_kv, d, page_size, max_pages,     \
         n_pool_pages, max_positions, append, status)

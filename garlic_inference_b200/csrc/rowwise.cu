@@ -15,6 +15,7 @@
 template <typename T>
 __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restrict__ table,
                                  float* __restrict__ out, int vocab, int hidden) {
+    gi_pdl_start();
     const int t = blockIdx.x;
     const int id = ids[t];
     float* dst = out + (size_t)t * hidden;
@@ -33,9 +34,9 @@ extern "C" int gi_embedding(const int* ids, const void* table, int table_dtype, 
     const int threads = hidden >= 1024 ? 256 : 128;
     cudaStream_t s = (cudaStream_t)stream;
     if (table_dtype == GI_DTYPE_F32)
-        embedding_kernel<float><<<n_tokens, threads, 0, s>>>(ids, (const float*)table, out, vocab, hidden);
+        gi_launch(embedding_kernel<float>, dim3(n_tokens), dim3(threads), 0, s, ids, (const float*)table, out, vocab, hidden);
     else if (table_dtype == GI_DTYPE_BF16)
-        embedding_kernel<bf16><<<n_tokens, threads, 0, s>>>(ids, (const bf16*)table, out, vocab, hidden);
+        gi_launch(embedding_kernel<bf16>, dim3(n_tokens), dim3(threads), 0, s, ids, (const bf16*)table, out, vocab, hidden);
     else
         GI_REQUIRE(false, "gi_embedding: table dtype %d is neither float32 nor bfloat16", table_dtype);
     return gi_check_launch("gi_embedding");
@@ -52,6 +53,7 @@ template <typename T>
 __global__ void add_rmsnorm_kernel(const T* __restrict__ delta, float* __restrict__ residual,
                                    const void* __restrict__ weight, int w_dtype, T* __restrict__ out,
                                    const int* __restrict__ rows, int dim, float eps, int write_residual) {
+    gi_pdl_start();
     __shared__ float red[33];
     const int r = blockIdx.x;
     const size_t i = rows ? (size_t)rows[r] : (size_t)r;
@@ -84,10 +86,10 @@ extern "C" int gi_add_rmsnorm(const void* delta, float* residual, const void* we
     const int threads = dim >= 2048 ? 512 : (dim >= 512 ? 256 : (dim >= 128 ? 128 : 32));
     cudaStream_t s = (cudaStream_t)stream;
     if (act_dtype == GI_DTYPE_F32)
-        add_rmsnorm_kernel<float><<<n_rows, threads, 0, s>>>((const float*)delta, residual, weight, w_dtype,
+        gi_launch(add_rmsnorm_kernel<float>, dim3(n_rows), dim3(threads), 0, s, (const float*)delta, residual, weight, w_dtype,
                                                              (float*)out, rows, dim, eps, write_residual);
     else if (act_dtype == GI_DTYPE_BF16)
-        add_rmsnorm_kernel<bf16><<<n_rows, threads, 0, s>>>((const bf16*)delta, residual, weight, w_dtype,
+        gi_launch(add_rmsnorm_kernel<bf16>, dim3(n_rows), dim3(threads), 0, s, (const bf16*)delta, residual, weight, w_dtype,
                                                             (bf16*)out, rows, dim, eps, write_residual);
     else
         GI_REQUIRE(false, "gi_add_rmsnorm: activation dtype %d", act_dtype);
@@ -97,6 +99,7 @@ extern "C" int gi_add_rmsnorm(const void* delta, float* residual, const void* we
 // residual[i] += delta[i] (float32 sum), for arrangements that need the stream itself.
 template <typename T>
 __global__ void residual_add_kernel(const T* __restrict__ delta, float* __restrict__ residual, size_t n) {
+    gi_pdl_start();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (; i < n; i += stride) residual[i] += to_f32(delta[i]);
@@ -109,9 +112,9 @@ extern "C" int gi_residual_add(const void* delta, int act_dtype, float* residual
     const int blocks = (int)((n + threads - 1) / threads < 4096 ? (n + threads - 1) / threads : 4096);
     cudaStream_t s = (cudaStream_t)stream;
     if (act_dtype == GI_DTYPE_F32)
-        residual_add_kernel<float><<<blocks, threads, 0, s>>>((const float*)delta, residual, (size_t)n);
+        gi_launch(residual_add_kernel<float>, dim3(blocks), dim3(threads), 0, s, (const float*)delta, residual, (size_t)n);
     else if (act_dtype == GI_DTYPE_BF16)
-        residual_add_kernel<bf16><<<blocks, threads, 0, s>>>((const bf16*)delta, residual, (size_t)n);
+        gi_launch(residual_add_kernel<bf16>, dim3(blocks), dim3(threads), 0, s, (const bf16*)delta, residual, (size_t)n);
     else
         GI_REQUIRE(false, "gi_residual_add: activation dtype %d", act_dtype);
     return gi_check_launch("gi_residual_add");
@@ -122,6 +125,7 @@ extern "C" int gi_residual_add(const void* delta, int act_dtype, float* residual
 // projection in the last.  out[n, inter] = silu(gate) * up, in float32, rounded once.
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, size_t total) {
+    gi_pdl_start();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (; i < total; i += stride) {
@@ -136,6 +140,7 @@ __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out
 // bfloat16, 8 columns a thread (inter must be a multiple of 8)
 __global__ void swiglu_bf16x8_kernel(const bf16* __restrict__ gate_up, bf16* __restrict__ out, int inter,
                                      size_t total_vec) {
+    gi_pdl_start();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     const int vec_per_row = inter / 8;
@@ -167,14 +172,14 @@ extern "C" int gi_swiglu(const void* gate_up, void* out, int act_dtype, int n_ro
     if (act_dtype == GI_DTYPE_BF16 && inter % 8 == 0) {
         const size_t nv = total / 8;
         const int blocks = (int)((nv + threads - 1) / threads < 65535 ? (nv + threads - 1) / threads : 65535);
-        swiglu_bf16x8_kernel<<<blocks, threads, 0, s>>>((const bf16*)gate_up, (bf16*)out, inter, nv);
+        gi_launch(swiglu_bf16x8_kernel, dim3(blocks), dim3(threads), 0, s, (const bf16*)gate_up, (bf16*)out, inter, nv);
         return gi_check_launch("gi_swiglu");
     }
     const int blocks = (int)((total + threads - 1) / threads < 65535 ? (total + threads - 1) / threads : 65535);
     if (act_dtype == GI_DTYPE_F32)
-        swiglu_kernel<float><<<blocks, threads, 0, s>>>((const float*)gate_up, (float*)out, inter, total);
+        gi_launch(swiglu_kernel<float>, dim3(blocks), dim3(threads), 0, s, (const float*)gate_up, (float*)out, inter, total);
     else if (act_dtype == GI_DTYPE_BF16)
-        swiglu_kernel<bf16><<<blocks, threads, 0, s>>>((const bf16*)gate_up, (bf16*)out, inter, total);
+        gi_launch(swiglu_kernel<bf16>, dim3(blocks), dim3(threads), 0, s, (const bf16*)gate_up, (bf16*)out, inter, total);
     else
         GI_REQUIRE(false, "gi_swiglu: activation dtype %d", act_dtype);
     return gi_check_launch("gi_swiglu");
@@ -183,6 +188,7 @@ extern "C" int gi_swiglu(const void* gate_up, void* out, int act_dtype, int n_ro
 // -------------------------------------------------------------------- casts
 template <typename S, typename D>
 __global__ void cast_kernel(const S* __restrict__ src, D* __restrict__ dst, size_t n) {
+    gi_pdl_start();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (; i < n; i += stride) dst[i] = from_f32<D>(to_f32(src[i]));
@@ -195,9 +201,9 @@ extern "C" int gi_cast(const void* src, int src_dtype, void* dst, int dst_dtype,
     const int blocks = (int)((n + threads - 1) / threads < 65535 ? (n + threads - 1) / threads : 65535);
     cudaStream_t s = (cudaStream_t)stream;
     if (src_dtype == GI_DTYPE_F32 && dst_dtype == GI_DTYPE_BF16)
-        cast_kernel<float, bf16><<<blocks, threads, 0, s>>>((const float*)src, (bf16*)dst, (size_t)n);
+        gi_launch(cast_kernel<float, bf16>, dim3(blocks), dim3(threads), 0, s, (const float*)src, (bf16*)dst, (size_t)n);
     else if (src_dtype == GI_DTYPE_BF16 && dst_dtype == GI_DTYPE_F32)
-        cast_kernel<bf16, float><<<blocks, threads, 0, s>>>((const bf16*)src, (float*)dst, (size_t)n);
+        gi_launch(cast_kernel<bf16, float>, dim3(blocks), dim3(threads), 0, s, (const bf16*)src, (float*)dst, (size_t)n);
     else
         GI_REQUIRE(false, "gi_cast: from dtype %d to dtype %d", src_dtype, dst_dtype);
     return gi_check_launch("gi_cast");

@@ -12,6 +12,7 @@ from typing import Optional
 import torch
 
 from .library import KernelError, check, counters, require_gpu
+from .library import counters as counters_mod
 
 F32, BF16 = 0, 1
 _CODES = {torch.float32: F32, torch.bfloat16: BF16}
@@ -243,8 +244,12 @@ def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor], streams: O
     if out is None:
         out = torch.empty((n,), dtype=torch.int32, device=logits.device)
     _dense(out, "out", torch.int32)
+    n_chunks = l.gi_sample_chunks(vocab)
+    part_v = torch.empty((n * n_chunks,), dtype=torch.float32, device=logits.device)
+    part_i = torch.empty((n * n_chunks,), dtype=torch.int32, device=logits.device)
     check(l.gi_sample(_ptr(logits), logits.stride(0), n, vocab, _ptr(temperature), _ptr(streams), _ptr(counters),
-                      int(seed) & 0xFFFFFFFFFFFFFFFF, _ptr(out), _stream()), l)
+                      int(seed) & 0xFFFFFFFFFFFFFFFF, _ptr(part_v), _ptr(part_i), _ptr(out), _stream()), l)
+    counters_mod.launches += 1                               # the second pass
     return out
 
 
@@ -275,9 +280,12 @@ def attention_prefill_bf16(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.
 
 
 def decode_splits(n_seqs: int, n_kv: int) -> int:
-    """Slices of the keys per (sequence, key/value head) in the decode kernel: enough CTAs to fill the
-    GPU a few times over at small batches, one slice once the batch alone does."""
-    return max(1, min(32, -(-1184 // max(1, n_seqs * n_kv))))
+    """Slices of the keys per (sequence, key/value head) in the decode kernel.  Measured on a B200:
+    about 256 CTAs are wanted at small batches (but at most 16 slices), and two slices still pay
+    when the batch alone makes a few hundred CTAs, because they even out the last wave."""
+    pairs = max(1, n_seqs * n_kv)
+    n = max(1, min(16, -(-256 // pairs)))
+    return 2 if n == 1 and pairs < 1776 else n
 
 
 def attention_decode_bf16(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: torch.Tensor,
