@@ -1,0 +1,142 @@
+"""Single kernels at the benchmark model's sizes, for timing and for profilers.
+
+    python -m garlic_inference_b200.ops.microbench run  OP M [SHAPE]     a few plain launches (what ncu captures)
+    python -m garlic_inference_b200.ops.microbench time [linear|attn]    GPU time inside CUDA graphs, cold L2
+
+OP: gemv | skinny | cublas (M = rows of x, SHAPE = qkv | o | gate_up | down | lm_head at Qwen3-8B sizes),
+attn_decode (M = sequences, 2,048 cached tokens each), attn_prefill (M = prompt length).
+`time` rotates over several copies of the operands (more than the 126 MB of L2) and reports the
+algorithmic bytes over the time.
+"""
+from __future__ import annotations
+
+import sys
+
+import torch
+
+from . import kernels
+
+SHAPES = {"qkv": (6144, 4096), "o": (4096, 4096), "gate_up": (24576, 4096), "down": (4096, 12288),
+          "lm_head": (151936, 4096)}
+N_Q, N_KV, HEAD_DIM, PAGE = 32, 8, 128, 64
+DEV = "cuda"
+
+
+def graph_time(fns, reps: int = 5) -> float:
+    """Milliseconds per call of the callables captured back to back in one CUDA graph."""
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for f in fns:
+            f()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for f in fns:
+            f()
+    graph.replay()
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(reps):
+        graph.replay()
+    end.record()
+    torch.cuda.synchronize()
+    return start.elapsed_time(end) / reps / len(fns)
+
+
+def _weights(shape: str, copies: int):
+    n, k = SHAPES[shape]
+    return [torch.randn(n, k, device=DEV, dtype=torch.bfloat16) * 0.02 for _ in range(copies)]
+
+
+def _linear(op: str, x, w):
+    if op == "gemv":
+        return kernels.gemv_bf16(x, w, torch.bfloat16)
+    if op == "skinny":
+        return kernels.gemm_skinny_bf16(x, w, torch.bfloat16)
+    if op == "cublas":
+        return torch.mm(x, w.t())
+    raise SystemExit(f"unknown op {op}")
+
+
+def _decode_case(batch: int, ctx: int, copies: int):
+    n_pages = batch * ctx // PAGE
+    pools = [(torch.randn(n_pages, N_KV, PAGE, HEAD_DIM, device=DEV, dtype=torch.bfloat16),
+              torch.randn(n_pages, N_KV, PAGE, HEAD_DIM, device=DEV, dtype=torch.bfloat16)) for _ in range(copies)]
+    table = torch.arange(n_pages, dtype=torch.int32, device=DEV).view(batch, -1)
+    q = torch.randn(batch, N_Q, HEAD_DIM, device=DEV, dtype=torch.bfloat16)
+    pos = torch.full((batch,), ctx - 1, dtype=torch.int32, device=DEV)
+    slot = torch.arange(batch, dtype=torch.int32, device=DEV)
+    return pools, table, q, pos, slot
+
+
+def run(op: str, m: int, shape: str = "gate_up") -> None:
+    if op in ("gemv", "skinny", "cublas"):
+        ws = _weights(shape, 3)
+        x = torch.randn(m, SHAPES[shape][1], device=DEV, dtype=torch.bfloat16)
+        for i in range(6):
+            _linear(op, x, ws[i % 3])
+    elif op == "attn_decode":
+        pools, table, q, pos, slot = _decode_case(m, 2048, 2)
+        for i in range(6):
+            kernels.attention_decode_bf16(q, pools[i % 2][0], pools[i % 2][1], table, pos, slot, HEAD_DIM ** -0.5, 0)
+    elif op == "attn_prefill":
+        n_pages = -(-m // PAGE)
+        k_pool = torch.randn(n_pages, N_KV, PAGE, HEAD_DIM, device=DEV, dtype=torch.bfloat16)
+        v_pool = torch.randn_like(k_pool)
+        table = torch.arange(n_pages, dtype=torch.int32, device=DEV).view(1, -1)
+        q = torch.randn(m, N_Q, HEAD_DIM, device=DEV, dtype=torch.bfloat16)
+        tiles = torch.tensor([(0, r, min(64, m - r), r) for r in range(0, m, 64)], dtype=torch.int32, device=DEV)
+        for _ in range(4):
+            kernels.attention_prefill_bf16(q, k_pool, v_pool, table, tiles, HEAD_DIM ** -0.5, 0)
+    else:
+        raise SystemExit(f"unknown op {op}")
+    torch.cuda.synchronize()
+    print("ok")
+
+
+def time_linear() -> None:
+    for shape, (n, k) in SHAPES.items():
+        copies = 2 if shape == "lm_head" else max(3, int(500e6 // (n * k * 2)) + 1)
+        ws = _weights(shape, copies)
+        for m in (1, 2, 4, 8, 16, 64):
+            x = torch.randn(m, k, device=DEV, dtype=torch.bfloat16)
+            ops = (["gemv"] if m <= 8 else []) + (["skinny"] if m <= 16 else []) + ["cublas"]
+            res = {op: graph_time([(lambda w=w, op=op: _linear(op, x, w)) for w in ws]) for op in ops}
+            print(f"{shape:8s} M={m:3d}  " + "  ".join(f"{op}: {ms * 1e3:7.1f} us {n * k * 2 / ms / 1e6:5.0f} GB/s"
+                                                        for op, ms in res.items()), flush=True)
+        del ws
+
+
+def time_attention() -> None:
+    for batch in (1, 8, 64):
+        for ctx in (2048, 4096):
+            nbytes = batch * ctx * N_KV * HEAD_DIM * 2 * 2
+            copies = min(40, max(3, int(500e6 // nbytes) + 1))
+            pools, table, q, pos, slot = _decode_case(batch, ctx, copies)
+            ms = graph_time([(lambda p=p: kernels.attention_decode_bf16(q, p[0], p[1], table, pos, slot,
+                                                                         HEAD_DIM ** -0.5, 0)) for p in pools])
+            print(f"attn_decode batch={batch:3d} ctx={ctx}  {ms * 1e3:7.1f} us  {nbytes / ms / 1e6:5.0f} GB/s "
+                  f"(slices {kernels.decode_splits(batch, N_KV)})", flush=True)
+            del pools
+
+
+def main(argv) -> int:
+    if len(argv) >= 3 and argv[0] == "run":
+        run(argv[1], int(argv[2]), argv[3] if len(argv) > 3 else "gate_up")
+    elif argv and argv[0] == "time":
+        which = argv[1] if len(argv) > 1 else "all"
+        if which in ("all", "linear"):
+            time_linear()
+        if which in ("all", "attn"):
+            time_attention()
+    else:
+        print(__doc__)
+        return 2
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main(sys.argv[1:]))
