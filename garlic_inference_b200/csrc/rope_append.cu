@@ -95,6 +95,75 @@ __global__ void qk_norm_rope_append_kernel(
     }
 }
 
+// The same for heads whose size is a multiple of 64 (up to 256) with the whole head rotated: a lane
+// holds EPL = d/32 consecutive elements, so that loads and stores are contiguous over the warp and the
+// rotation partner of lane l (the element half a head away) sits in lane l ^ 16.
+template <typename T, int EPL>
+__global__ void qk_norm_rope_append_vec_kernel(
+    const T* __restrict__ qkv, T* __restrict__ q_out, T* __restrict__ k_pool, T* __restrict__ v_pool,
+    const void* __restrict__ q_w, const void* __restrict__ k_w, int w_dtype, float eps,
+    const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+    const int* __restrict__ tok_pos, const int* __restrict__ tok_slot, const int* __restrict__ block_table,
+    int n_tokens, int n_q, int n_kv, int page_size, int max_pages, int n_pool_pages,
+    int max_positions, int append, int* __restrict__ status) {
+    gi_pdl_start();
+    constexpr int d = EPL * 32, half = d / 2;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int heads_here = append ? n_q + 2 * n_kv : n_q;
+    const long long item = (long long)blockIdx.x * ROPE_WARPS + warp;
+    if (item >= (long long)n_tokens * heads_here) return;
+    const int t = (int)(item / heads_here);
+    const int h = (int)(item - (long long)t * heads_here);
+    const T* src = qkv + (size_t)t * (n_q + 2 * n_kv) * d + (size_t)h * d + lane * EPL;
+    const bool is_q = h < n_q;
+    const bool is_k = !is_q && h < n_q + n_kv;
+    const int kvh = is_q ? 0 : (is_k ? h - n_q : h - n_q - n_kv);
+    T* dst;
+    const int pos = tok_pos[t];
+    if (is_q) {
+        dst = q_out + ((size_t)t * n_q + h) * d;
+    } else {
+        const int slot = tok_slot[t];
+        if (slot < 0) return;
+        const int lp = pos / page_size;
+        if (pos < 0 || lp >= max_pages) { if (lane == 0) atomicExch(status, 1); return; }
+        const int page = block_table[(size_t)slot * max_pages + lp];
+        if (page < 0 || page >= n_pool_pages) { if (lane == 0) atomicExch(status, 2); return; }
+        dst = (is_k ? k_pool : v_pool) + (((size_t)page * n_kv + kvh) * page_size + (pos - lp * page_size)) * d;
+    }
+    dst += lane * EPL;
+    T raw[EPL];
+#pragma unroll
+    for (int e = 0; e < EPL; e += 2) {           // EPL is even: two elements (4 or 8 bytes) at a time
+        raw[e] = src[e];
+        raw[e + 1] = src[e + 1];
+    }
+    if (!is_q && !is_k) {                        // values: copy
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) dst[e] = raw[e];
+        return;
+    }
+    float x[EPL];
+    float ss = 0.f;
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) { x[e] = to_f32(raw[e]); ss += x[e] * x[e]; }
+    const void* w = is_q ? q_w : k_w;
+    if (w) {
+        const float inv = rsqrtf(warp_sum(ss) / (float)d + eps);
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) x[e] = x[e] * inv * load_w(w, w_dtype, lane * EPL + e);
+    }
+    if (pos < 0 || pos >= max_positions) { if (lane == 0) atomicExch(status, 3); return; }
+    const float* cs = cos_t + (size_t)pos * half + (lane & 15) * EPL;
+    const float* sn = sin_t + (size_t)pos * half + (lane & 15) * EPL;
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) {
+        const float other = __shfl_xor_sync(0xffffffffu, x[e], 16);
+        const float y = lane < 16 ? x[e] * cs[e] - other * sn[e] : x[e] * cs[e] + other * sn[e];
+        dst[e] = from_f32<T>(y);
+    }
+}
+
 extern "C" int gi_qk_norm_rope_append(
     const void* qkv, void* q_out, void* k_pool, void* v_pool, int act_dtype,
     const void* q_w, const void* k_w, int w_dtype, float eps,
@@ -115,6 +184,26 @@ extern "C" int gi_qk_norm_rope_append(
     GI_REQUIRE(blocks < 2147483647LL, "gi_qk_norm_rope_append: too many (token, head) pairs");
     const size_t smem = (size_t)ROPE_WARPS * d * sizeof(float);
     cudaStream_t s = (cudaStream_t)stream;
+    if (d % 64 == 0 && d <= 256 && rotary_dim == d) {
+#define LAUNCH_VEC(T, EPL)                                                                                      \
+    gi_launch(qk_norm_rope_append_vec_kernel<T, EPL>, dim3((int)blocks), dim3(ROPE_WARPS * 32), 0, s,           \
+              (const T*)qkv, (T*)q_out, (T*)k_pool, (T*)v_pool, q_w, k_w, w_dtype, eps, cos_t, sin_t, tok_pos,  \
+              tok_slot, block_table, n_tokens, n_q, n_kv, page_size, max_pages, n_pool_pages, max_positions,    \
+              append, status)
+#define LAUNCH_VEC_T(T)                                                                                         \
+    switch (d / 32) {                                                                                           \
+        case 2: LAUNCH_VEC(T, 2); break;                                                                        \
+        case 4: LAUNCH_VEC(T, 4); break;                                                                        \
+        case 6: LAUNCH_VEC(T, 6); break;                                                                        \
+        default: LAUNCH_VEC(T, 8); break;                                                                       \
+    }
+        if (act_dtype == GI_DTYPE_F32) { LAUNCH_VEC_T(float) }
+        else if (act_dtype == GI_DTYPE_BF16) { LAUNCH_VEC_T(bf16) }
+        else GI_REQUIRE(false, "gi_qk_norm_rope_append: activation dtype %d", act_dtype);
+#undef LAUNCH_VEC_T
+#undef LAUNCH_VEC
+        return gi_check_launch("gi_qk_norm_rope_append");
+    }
 #define LAUNCH(T)                                                                                     \
     gi_launch(qk_norm_rope_append_kernel<T>, dim3((int)blocks), dim3(ROPE_WARPS * 32), smem, s,                          \
         (const T*)qkv, (T*)q_out, (T*)k_pool, (T*)v_pool, q_w, k_w, w_dtype, eps, cos_t, sin_t,       \

@@ -76,6 +76,71 @@ __global__ void add_rmsnorm_kernel(const T* __restrict__ delta, float* __restric
     }
 }
 
+// The same with the row held in registers: one read of the inputs, four elements per thread and load.
+// Taken when dim is a multiple of 4 and at most 8,192; the thread count depends on dim alone.
+#define NORM_VEC_MAX_IT 8
+__device__ __forceinline__ float4 load4_f32(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4_act(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4_act(const bf16* p) {
+    const uint2 v = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void store4_act(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4_act(bf16* p, float4 v) {
+    uint2 o;
+    *reinterpret_cast<__nv_bfloat162*>(&o.x) = __floats2bfloat162_rn(v.x, v.y);
+    *reinterpret_cast<__nv_bfloat162*>(&o.y) = __floats2bfloat162_rn(v.z, v.w);
+    *reinterpret_cast<uint2*>(p) = o;
+}
+__device__ __forceinline__ float4 load4_w(const void* w, int w_dtype, int c) {
+    return w_dtype == GI_DTYPE_F32 ? load4_f32((const float*)w + c) : load4_act((const bf16*)w + c);
+}
+
+template <typename T>
+__global__ void add_rmsnorm_vec_kernel(const T* __restrict__ delta, float* __restrict__ residual,
+                                       const void* __restrict__ weight, int w_dtype, T* __restrict__ out,
+                                       const int* __restrict__ rows, int dim, float eps, int write_residual) {
+    gi_pdl_start();
+    __shared__ float red[33];
+    const int r = blockIdx.x;
+    const size_t i = rows ? (size_t)rows[r] : (size_t)r;
+    float* res = residual + i * dim;
+    const T* del = delta ? delta + i * dim : nullptr;
+    float4 v[NORM_VEC_MAX_IT];
+    float ss = 0.f;
+#pragma unroll
+    for (int it = 0; it < NORM_VEC_MAX_IT; ++it) {
+        const int c = (it * blockDim.x + threadIdx.x) * 4;
+        if (c < dim) {
+            float4 s = load4_f32(res + c);
+            if (del) {
+                const float4 d4 = load4_act(del + c);
+                s.x += d4.x; s.y += d4.y; s.z += d4.z; s.w += d4.w;
+                if (write_residual) *reinterpret_cast<float4*>(res + c) = s;
+            }
+            v[it] = s;
+            ss += s.x * s.x;                     // the same order of additions whatever the batch is
+            ss += s.y * s.y;
+            ss += s.z * s.z;
+            ss += s.w * s.w;
+        }
+    }
+    ss = block_sum(ss, red);
+    const float inv = rsqrtf(ss / (float)dim + eps);
+    T* o = out + (size_t)r * dim;
+#pragma unroll
+    for (int it = 0; it < NORM_VEC_MAX_IT; ++it) {
+        const int c = (it * blockDim.x + threadIdx.x) * 4;
+        if (c < dim) {
+            const float4 w4 = load4_w(weight, w_dtype, c);
+            store4_act(o + c, make_float4(v[it].x * inv * w4.x, v[it].y * inv * w4.y, v[it].z * inv * w4.z,
+                                          v[it].w * inv * w4.w));
+        }
+    }
+}
+
 extern "C" int gi_add_rmsnorm(const void* delta, float* residual, const void* weight, int w_dtype,
                               void* out, int act_dtype, const int* rows, int n_rows, int dim,
                               float eps, int write_residual, void* stream) {
@@ -83,8 +148,23 @@ extern "C" int gi_add_rmsnorm(const void* delta, float* residual, const void* we
     GI_REQUIRE(w_dtype == GI_DTYPE_F32 || w_dtype == GI_DTYPE_BF16, "gi_add_rmsnorm: weight dtype %d", w_dtype);
     GI_REQUIRE(!(rows && write_residual), "gi_add_rmsnorm: gathered rows cannot write the residual back");
     if (n_rows == 0) return 0;
-    const int threads = dim >= 2048 ? 512 : (dim >= 512 ? 256 : (dim >= 128 ? 128 : 32));
     cudaStream_t s = (cudaStream_t)stream;
+    const bool aligned = ((uintptr_t)residual % 16 == 0) && ((uintptr_t)out % 16 == 0) && ((uintptr_t)weight % 16 == 0) &&
+                         ((uintptr_t)delta % 16 == 0);
+    if (dim % 4 == 0 && dim <= 256 * 4 * NORM_VEC_MAX_IT && aligned) {
+        int threads = ((dim / 4 + 31) / 32) * 32;
+        threads = threads > 256 ? 256 : threads;
+        if (act_dtype == GI_DTYPE_F32)
+            gi_launch(add_rmsnorm_vec_kernel<float>, dim3(n_rows), dim3(threads), 0, s, (const float*)delta, residual,
+                      weight, w_dtype, (float*)out, rows, dim, eps, write_residual);
+        else if (act_dtype == GI_DTYPE_BF16)
+            gi_launch(add_rmsnorm_vec_kernel<bf16>, dim3(n_rows), dim3(threads), 0, s, (const bf16*)delta, residual,
+                      weight, w_dtype, (bf16*)out, rows, dim, eps, write_residual);
+        else
+            GI_REQUIRE(false, "gi_add_rmsnorm: activation dtype %d", act_dtype);
+        return gi_check_launch("gi_add_rmsnorm");
+    }
+    const int threads = dim >= 2048 ? 512 : (dim >= 512 ? 256 : (dim >= 128 ? 128 : 32));
     if (act_dtype == GI_DTYPE_F32)
         gi_launch(add_rmsnorm_kernel<float>, dim3(n_rows), dim3(threads), 0, s, (const float*)delta, residual, weight, w_dtype,
                                                              (float*)out, rows, dim, eps, write_residual);

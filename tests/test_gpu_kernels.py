@@ -283,7 +283,9 @@ def test_attention_generic_same_bits_in_any_batch_and_any_pages():
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("n_q,n_kv,d,rot,qk_norm,wdt", [
     (4, 2, 16, 16, True, torch.bfloat16), (6, 1, 32, 32, True, torch.float32), (5, 5, 48, 48, True, torch.float32),
-    (3, 1, 64, 32, True, torch.float32), (2, 2, 128, 128, False, torch.float32), (2, 1, 80, 0, False, torch.float32)])
+    (3, 1, 64, 32, True, torch.float32), (2, 2, 128, 128, False, torch.float32), (2, 1, 80, 0, False, torch.float32),
+    (4, 2, 64, 64, True, torch.bfloat16), (8, 2, 128, 128, True, torch.bfloat16), (2, 1, 192, 192, True, torch.float32),
+    (2, 2, 256, 256, True, torch.float32)])
 def test_qk_norm_rope_append(dtype, n_q, n_kv, d, rot, qk_norm, wdt):
     import plain_qwen3 as plain
     from garlic_inference_b200.parts.rotary import RotaryPositions
