@@ -1,0 +1,287 @@
+// bfloat16 product for many rows (prompts): out[M,N] = x[M,K] . W[N,K]^T on the fifth-generation
+// tensor cores.
+//
+// One CTA computes a 128 x 256 tile of the output.  Its six warps have three jobs:
+//   warp 0, one lane:  TMA.  For every 64-wide slice of K it brings the 128 x 64 tile of x and the
+//                      256 x 64 tile of W into one of four shared-memory stages (tensor maps with the
+//                      128-byte swizzle, which is the layout the tensor core reads) and arms the
+//                      stage's "full" mbarrier with the byte count.
+//   warp 1, one lane:  MMA.  It waits for a stage, issues four tcgen05.mma (128 x 256 x 16 each) that
+//                      accumulate in tensor memory (256 columns of float32, allocated by this warp),
+//                      and commits them to the stage's "empty" mbarrier so the TMA lane may refill it;
+//                      after the last slice it commits to the "accumulator ready" mbarrier.
+//   warps 2..5:        epilogue.  Each reads its 32 lanes of tensor memory with tcgen05.ld, 32 columns
+//                      at a time, rounds to the output type and stores.
+// Rows of x beyond M and columns beyond N or K are zero-filled by the TMA unit and never stored.
+//
+// Every wait on an mbarrier is bounded.  When a wait runs out the kernel records a code in
+// *error_flag, all roles leave their loops, the copies still in flight are waited for (bounded again),
+// tensor memory is freed and the kernel returns; the output is then unspecified.
+//
+// Upstream calls a library product for every size (src/src-cuda/mat-ops/gemm/gemm.cu:22-41).
+#include "common.cuh"
+
+#include <cuda.h>
+
+#define TG_BM 128
+#define TG_BN 256
+#define TG_BK 64
+#define TG_STAGES 4
+#define TG_THREADS 192
+#define TG_A_BYTES (TG_BM * TG_BK * 2)
+#define TG_B_BYTES (TG_BN * TG_BK * 2)
+#define TG_TMEM_COLS 256
+#define TG_SPIN_LIMIT (1 << 22)
+
+#define TG_ERR_PRODUCER 11
+#define TG_ERR_MMA 12
+#define TG_ERR_EPILOGUE 13
+
+struct TgControl {
+    unsigned long long full[TG_STAGES];
+    unsigned long long empty[TG_STAGES];
+    unsigned long long accum;
+    unsigned int tmem_base;
+    int abort;
+};
+
+__device__ __forceinline__ uint32_t tg_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void tg_mbar_init(void* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(tg_smem(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void tg_mbar_expect_tx(void* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(tg_smem(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool tg_mbar_try(void* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                 "selp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(tg_smem(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait: false when the limit ran out or another role gave up.
+__device__ __forceinline__ bool tg_mbar_wait(void* bar, uint32_t parity, volatile int* abort) {
+    for (int i = 0; i < TG_SPIN_LIMIT; ++i) {
+        if (tg_mbar_try(bar, parity)) return true;
+        if ((i & 255) == 255 && *abort) return false;
+    }
+    return false;
+}
+__device__ __forceinline__ void tg_tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, void* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(tg_smem(dst)), "l"(map), "r"(tg_smem(bar)), "r"(x), "r"(y) : "memory");
+}
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, stored with the 128-byte
+// swizzle in groups of 8 rows (1,024 bytes apart): start address, leading offset 1 (unused with a
+// swizzle), stride offset 1,024 bytes, descriptor version 1, layout type 2 = 128-byte swizzle.
+__device__ __forceinline__ uint64_t tg_smem_desc(uint32_t addr) {
+    return (uint64_t)((addr & 0x3FFFF) >> 4) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+__device__ __forceinline__ void tg_mma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "setp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tg_commit(void* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(tg_smem(bar)) : "memory");
+}
+__device__ __forceinline__ void tg_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+template <int OUT_F32>
+__global__ void __launch_bounds__(TG_THREADS, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                    void* __restrict__ out, int M, int N, int K, int* __restrict__ error_flag) {
+    gi_pdl_start();
+    extern __shared__ unsigned char tg_raw[];
+    unsigned char* smem = (unsigned char*)(((uintptr_t)tg_raw + 1023) & ~(uintptr_t)1023);   // the swizzle wants 1,024-byte tiles
+    unsigned char* a_tiles = smem;
+    unsigned char* b_tiles = smem + TG_STAGES * TG_A_BYTES;
+    TgControl* ctl = reinterpret_cast<TgControl*>(smem + TG_STAGES * (TG_A_BYTES + TG_B_BYTES));
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.y * TG_BM, n0 = blockIdx.x * TG_BN;
+    const int k_tiles = (K + TG_BK - 1) / TG_BK;
+    volatile int* abort = &ctl->abort;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < TG_STAGES; ++s) { tg_mbar_init(&ctl->full[s], 1); tg_mbar_init(&ctl->empty[s], 1); }
+        tg_mbar_init(&ctl->accum, 1);
+        ctl->abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {                             // this warp owns the tensor memory: allocates it now, frees it at the end
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(tg_smem(&ctl->tmem_base)), "r"(TG_TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = ctl->tmem_base;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int armed = 0;                       // slices whose copies were issued
+            for (int kt = 0; kt < k_tiles; ++kt) {
+                const int s = kt % TG_STAGES;
+                if (!tg_mbar_wait(&ctl->empty[s], ((kt / TG_STAGES) & 1) ^ 1, abort)) {
+                    if (!*abort) { *abort = 1; atomicExch(error_flag, TG_ERR_PRODUCER); }
+                    break;
+                }
+                tg_mbar_expect_tx(&ctl->full[s], TG_A_BYTES + TG_B_BYTES);
+                tg_tma_load_2d(a_tiles + s * TG_A_BYTES, &map_x, kt * TG_BK, m0, &ctl->full[s]);
+                tg_tma_load_2d(b_tiles + s * TG_B_BYTES, &map_w, kt * TG_BK, n0, &ctl->full[s]);
+                armed = kt + 1;
+            }
+            if (*abort) {                        // let the copies still in flight land before the CTA leaves
+                int never = 0;
+                for (int kt = max(0, armed - TG_STAGES); kt < armed; ++kt)
+                    tg_mbar_wait(&ctl->full[kt % TG_STAGES], (kt / TG_STAGES) & 1, &never);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // instruction descriptor: float32 accumulate, bfloat16 a and b, both K-major, N = 256, M = 128
+            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TG_BN >> 3) << 17) | ((uint32_t)(TG_BM >> 4) << 24);
+            bool ok = true;
+            for (int kt = 0; kt < k_tiles && ok; ++kt) {
+                const int s = kt % TG_STAGES;
+                if (!tg_mbar_wait(&ctl->full[s], (kt / TG_STAGES) & 1, abort)) {
+                    if (!*abort) { *abort = 1; atomicExch(error_flag, TG_ERR_MMA); }
+                    ok = false;
+                    break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t a_addr = tg_smem(a_tiles + s * TG_A_BYTES), b_addr = tg_smem(b_tiles + s * TG_B_BYTES);
+#pragma unroll
+                for (int k = 0; k < TG_BK / 16; ++k)     // 16 elements = 32 bytes further along K inside the swizzled row
+                    tg_mma(tmem, tg_smem_desc(a_addr + k * 32), tg_smem_desc(b_addr + k * 32), idesc, (kt | k) != 0);
+                tg_commit(&ctl->empty[s]);               // arrives when these products have read the stage
+            }
+            if (ok) tg_commit(&ctl->accum);              // arrives when every product is done
+        }
+    } else {
+        const int q = warp & 3;                          // a warp reads the 32 lanes of tensor memory of its quarter
+        const bool ready = tg_mbar_wait(&ctl->accum, 0, abort);
+        if (!ready && !*abort) { *abort = 1; atomicExch(error_flag, TG_ERR_EPILOGUE); }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (ready) {
+            const int row = m0 + q * 32 + lane;
+#pragma unroll 1
+            for (int c = 0; c < TG_BN / 32; ++c) {
+                uint32_t r[32];
+                tg_ld32(tmem + ((uint32_t)(q * 32) << 16) + c * 32, r);
+                const int col = n0 + c * 32;
+                if (row < M && col < N) {
+                    if (OUT_F32) {
+                        float* dst = reinterpret_cast<float*>(out) + (size_t)row * N + col;
+                        if (col + 32 <= N && (N & 3) == 0) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 4)
+                                *reinterpret_cast<uint4*>(dst + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+                        } else {
+                            for (int j = 0; j < 32 && col + j < N; ++j) dst[j] = __uint_as_float(r[j]);
+                        }
+                    } else {
+                        bf16* dst = reinterpret_cast<bf16*>(out) + (size_t)row * N + col;
+                        if (col + 32 <= N && (N & 7) == 0) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 8) {
+                                uint4 v;
+                                __nv_bfloat162 p0 = __floats2bfloat162_rn(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
+                                __nv_bfloat162 p1 = __floats2bfloat162_rn(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                                __nv_bfloat162 p2 = __floats2bfloat162_rn(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5]));
+                                __nv_bfloat162 p3 = __floats2bfloat162_rn(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7]));
+                                v.x = *reinterpret_cast<uint32_t*>(&p0); v.y = *reinterpret_cast<uint32_t*>(&p1);
+                                v.z = *reinterpret_cast<uint32_t*>(&p2); v.w = *reinterpret_cast<uint32_t*>(&p3);
+                                *reinterpret_cast<uint4*>(dst + j) = v;
+                            }
+                        } else {
+                            for (int j = 0; j < 32 && col + j < N; ++j) dst[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
+                        }
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TG_TMEM_COLS) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------------------ host side
+typedef CUresult (*tg_encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                 const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static tg_encode_fn tg_encoder() {
+    static tg_encode_fn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (tg_encode_fn)p;
+    }
+    return fn;
+}
+
+// A [rows, K] row-major bfloat16 matrix as a 2-D tensor map with boxes of 64 x box_rows and the 128-byte swizzle.
+static int tg_make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) {
+    tg_encode_fn enc = tg_encoder();
+    GI_REQUIRE(enc != nullptr, "gi_gemm_tcgen05_bf16: the driver does not offer cuTensorMapEncodeTiled");
+    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+    const cuuint32_t box[2] = {TG_BK, (cuuint32_t)box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    GI_REQUIRE(r == CUDA_SUCCESS, "gi_gemm_tcgen05_bf16: cuTensorMapEncodeTiled failed with code %d", (int)r);
+    return 0;
+}
+
+// error_flag: an int on the device that the kernel sets when one of its bounded waits runs out (0 = fine).
+extern "C" int gi_gemm_tcgen05_bf16(const void* x, const void* W, void* out, int out_dtype, int M, int N, int K,
+                                    int* error_flag, void* stream) {
+    GI_REQUIRE(M > 0 && N > 0 && K > 0, "gi_gemm_tcgen05_bf16: sizes must be positive");
+    GI_REQUIRE(K % 8 == 0, "gi_gemm_tcgen05_bf16: inner size %d is no multiple of 8 (rows must be a multiple of 16 bytes for TMA)", K);
+    GI_REQUIRE(((uintptr_t)x % 16 == 0) && ((uintptr_t)W % 16 == 0) && ((uintptr_t)out % 16 == 0),
+               "gi_gemm_tcgen05_bf16: operands must start on 16 bytes");
+    GI_REQUIRE(out_dtype == GI_DTYPE_BF16 || out_dtype == GI_DTYPE_F32, "gi_gemm_tcgen05_bf16: output dtype %d", out_dtype);
+    GI_REQUIRE(error_flag != nullptr, "gi_gemm_tcgen05_bf16: an error flag on the device is required");
+    const long long gy = (M + TG_BM - 1) / TG_BM;
+    GI_REQUIRE(gy <= 65535, "gi_gemm_tcgen05_bf16: %d rows in one product is beyond %d", M, 65535 * TG_BM);
+    CUtensorMap map_x, map_w;
+    if (int rc = tg_make_map(&map_x, x, M, K, TG_BM)) return rc;
+    if (int rc = tg_make_map(&map_w, W, N, K, TG_BN)) return rc;
+    const size_t smem = (size_t)TG_STAGES * (TG_A_BYTES + TG_B_BYTES) + sizeof(TgControl) + 1024;
+    static bool attr_done[2] = {false, false};
+    const int f32 = out_dtype == GI_DTYPE_F32;
+    if (!attr_done[f32]) {
+        cudaError_t e = f32 ? cudaFuncSetAttribute((const void*)gemm_tcgen05_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+                            : cudaFuncSetAttribute((const void*)gemm_tcgen05_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) { gi_set_error("gi_gemm_tcgen05_bf16: shared memory: %s", cudaGetErrorString(e)); return (int)e; }
+        attr_done[f32] = true;
+    }
+    dim3 grid((N + TG_BN - 1) / TG_BN, (unsigned)gy);
+    if (f32) gi_launch(gemm_tcgen05_kernel<1>, grid, dim3(TG_THREADS), smem, (cudaStream_t)stream, map_x, map_w, out, M, N, K, error_flag);
+    else gi_launch(gemm_tcgen05_kernel<0>, grid, dim3(TG_THREADS), smem, (cudaStream_t)stream, map_x, map_w, out, M, N, K, error_flag);
+    return gi_check_launch("gi_gemm_tcgen05_bf16");
+}

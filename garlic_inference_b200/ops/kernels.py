@@ -222,6 +222,30 @@ def gemm_skinny_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, n
     return out
 
 
+_tcgen05_flag: dict = {}
+
+
+def tcgen05_error_flag(device) -> torch.Tensor:
+    """The int32 on `device` that the tcgen05 product sets when one of its bounded waits runs out."""
+    key = torch.device(device).index or 0
+    if key not in _tcgen05_flag:
+        _tcgen05_flag[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _tcgen05_flag[key]
+
+
+def gemm_tcgen05_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """x [M, K] . w[N, K]^T for many rows on tcgen05 tensor cores (TMA-fed, accumulators in tensor memory)."""
+    l = require_gpu()
+    _dense(x, "x", torch.bfloat16), _dense(w, "w", torch.bfloat16)
+    (m, k), (n, k2) = x.shape, w.shape
+    if k != k2:
+        raise KernelError(f"inner sizes differ: x {tuple(x.shape)}, w {tuple(w.shape)}")
+    out = torch.empty((m, n), dtype=out_dtype, device=x.device)
+    check(l.gi_gemm_tcgen05_bf16(_ptr(x), _ptr(w), _ptr(out), code(out_dtype), m, n, k,
+                                 _ptr(tcgen05_error_flag(x.device)), _stream()), l)
+    return out
+
+
 def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor], streams: Optional[torch.Tensor],
            counters: Optional[torch.Tensor], seed: int, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """One token per row of float32 logits [n, vocab]: greedy where temperature <= 0 (or None),

@@ -148,6 +148,25 @@ def test_gemm_skinny_bf16(m, n, k, split, wide):
     assert torch.equal(out32, K().gemm_skinny_bf16(x, w, torch.float32, n_split=split, wide=wide)), "same bits from run to run"
 
 
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (2048, 512, 256), (300, 1000, 4096), (1, 264, 72), (129, 257 * 8, 1288),
+                                   (2048, 6144, 4096)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_gemm_tcgen05_bf16(m, n, k, out_dtype):
+    g = torch.Generator(device=DEV).manual_seed(m + n + k)
+    x = torch.randn(m, k, generator=g, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(n, k, generator=g, device=DEV) * 0.1).to(torch.bfloat16)
+    flag = K().tcgen05_error_flag(x.device)
+    flag.zero_()
+    out = K().gemm_tcgen05_bf16(x, w, out_dtype)
+    torch.cuda.synchronize()
+    assert int(flag.item()) == 0, "a bounded wait of the kernel ran out"
+    ref = x.float() @ w.float().T
+    if out_dtype == torch.float32:
+        torch.testing.assert_close(out, ref, rtol=1e-4, atol=2e-4 * math.sqrt(k))
+    else:
+        torch.testing.assert_close(out.float(), ref.to(torch.bfloat16).float(), **ulp_tol(torch.bfloat16))
+
+
 def test_kernels_refuse_what_they_cannot_take():
     from garlic_inference_b200.ops import KernelError
     x = torch.zeros(9, 64, dtype=torch.bfloat16, device=DEV)
