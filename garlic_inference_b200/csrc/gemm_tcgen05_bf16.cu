@@ -1,7 +1,7 @@
 // bfloat16 product for many rows (prompts): out[M,N] = x[M,K] . W[N,K]^T on the fifth-generation
 // tensor cores.
 //
-// One CTA computes a 128 x 256 tile of the output.  Its six warps have three jobs:
+// One CTA per SM walks over 128 x 256 tiles of the output.  Its six warps have three jobs:
 //   warp 0, one lane:  TMA.  For every 64-wide slice of K it brings the 128 x 64 tile of x and the
 //                      256 x 64 tile of W into one of four shared-memory stages (tensor maps with the
 //                      128-byte swizzle, which is the layout the tensor core reads) and arms the
@@ -9,9 +9,11 @@
 //   warp 1, one lane:  MMA.  It waits for a stage, issues four tcgen05.mma (128 x 256 x 16 each) that
 //                      accumulate in tensor memory (256 columns of float32, allocated by this warp),
 //                      and commits them to the stage's "empty" mbarrier so the TMA lane may refill it;
-//                      after the last slice it commits to the "accumulator ready" mbarrier.
+//                      after the last slice it commits to the tile's "accumulator full" mbarrier.  There
+//                      are two accumulators (2 x 256 = all 512 columns), so the next tile's products run
+//                      while the epilogue drains the last one.
 //   warps 2..5:        epilogue.  Each reads its 32 lanes of tensor memory with tcgen05.ld, 32 columns
-//                      at a time, rounds to the output type and stores.
+//                      at a time, rounds to the output type, stores, and hands the accumulator back.
 // Rows of x beyond M and columns beyond N or K are zero-filled by the TMA unit and never stored.
 //
 // Every wait on an mbarrier is bounded.  When a wait runs out the kernel records a code in
@@ -30,7 +32,7 @@
 #define TG_THREADS 192
 #define TG_A_BYTES (TG_BM * TG_BK * 2)
 #define TG_B_BYTES (TG_BN * TG_BK * 2)
-#define TG_TMEM_COLS 256
+#define TG_TMEM_COLS 512          // two float32 accumulators of 256 columns
 #define TG_SPIN_LIMIT (1 << 22)
 
 #define TG_ERR_PRODUCER 11
@@ -40,7 +42,8 @@
 struct TgControl {
     unsigned long long full[TG_STAGES];
     unsigned long long empty[TG_STAGES];
-    unsigned long long accum;
+    unsigned long long acc_full[2];
+    unsigned long long acc_empty[2];
     unsigned int tmem_base;
     int abort;
 };
@@ -112,13 +115,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     TgControl* ctl = reinterpret_cast<TgControl*>(smem + TG_STAGES * (TG_A_BYTES + TG_B_BYTES));
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.y * TG_BM, n0 = blockIdx.x * TG_BN;
+    const int m_tiles = (M + TG_BM - 1) / TG_BM, n_tiles = (N + TG_BN - 1) / TG_BN;
+    const int total_tiles = m_tiles * n_tiles;
     const int k_tiles = (K + TG_BK - 1) / TG_BK;
     volatile int* abort = &ctl->abort;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < TG_STAGES; ++s) { tg_mbar_init(&ctl->full[s], 1); tg_mbar_init(&ctl->empty[s], 1); }
-        tg_mbar_init(&ctl->accum, 1);
+        for (int b = 0; b < 2; ++b) { tg_mbar_init(&ctl->acc_full[b], 1); tg_mbar_init(&ctl->acc_empty[b], 4); }
         ctl->abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -132,58 +136,81 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = ctl->tmem_base;
 
+    // A CTA walks the tiles blockIdx.x, blockIdx.x + gridDim.x, ...; tile t covers rows (t % m_tiles) and
+    // columns (t / m_tiles), so the CTAs that run together share a few W tiles (L2 holds them) and all of x.
     if (warp == 0) {
         if (lane == 0) {
-            int armed = 0;                       // slices whose copies were issued
-            for (int kt = 0; kt < k_tiles; ++kt) {
-                const int s = kt % TG_STAGES;
-                if (!tg_mbar_wait(&ctl->empty[s], ((kt / TG_STAGES) & 1) ^ 1, abort)) {
-                    if (!*abort) { *abort = 1; atomicExch(error_flag, TG_ERR_PRODUCER); }
-                    break;
+            int it = 0, armed = 0;               // slices so far over all tiles; slices whose copies were issued
+            bool ok = true;
+            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+                const int m0 = (t % m_tiles) * TG_BM, n0 = (t / m_tiles) * TG_BN;
+                for (int kt = 0; kt < k_tiles; ++kt, ++it) {
+                    const int s = it % TG_STAGES;
+                    if (!tg_mbar_wait(&ctl->empty[s], ((it / TG_STAGES) & 1) ^ 1, abort)) {
+                        if (!*abort) { *abort = 1; atomicExch(error_flag, TG_ERR_PRODUCER); }
+                        ok = false;
+                        break;
+                    }
+                    tg_mbar_expect_tx(&ctl->full[s], TG_A_BYTES + TG_B_BYTES);
+                    tg_tma_load_2d(a_tiles + s * TG_A_BYTES, &map_x, kt * TG_BK, m0, &ctl->full[s]);
+                    tg_tma_load_2d(b_tiles + s * TG_B_BYTES, &map_w, kt * TG_BK, n0, &ctl->full[s]);
+                    armed = it + 1;
                 }
-                tg_mbar_expect_tx(&ctl->full[s], TG_A_BYTES + TG_B_BYTES);
-                tg_tma_load_2d(a_tiles + s * TG_A_BYTES, &map_x, kt * TG_BK, m0, &ctl->full[s]);
-                tg_tma_load_2d(b_tiles + s * TG_B_BYTES, &map_w, kt * TG_BK, n0, &ctl->full[s]);
-                armed = kt + 1;
             }
             if (*abort) {                        // let the copies still in flight land before the CTA leaves
                 int never = 0;
-                for (int kt = max(0, armed - TG_STAGES); kt < armed; ++kt)
-                    tg_mbar_wait(&ctl->full[kt % TG_STAGES], (kt / TG_STAGES) & 1, &never);
+                for (int i = max(0, armed - TG_STAGES); i < armed; ++i)
+                    tg_mbar_wait(&ctl->full[i % TG_STAGES], (i / TG_STAGES) & 1, &never);
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             // instruction descriptor: float32 accumulate, bfloat16 a and b, both K-major, N = 256, M = 128
             const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TG_BN >> 3) << 17) | ((uint32_t)(TG_BM >> 4) << 24);
+            int it = 0, local = 0;
             bool ok = true;
-            for (int kt = 0; kt < k_tiles && ok; ++kt) {
-                const int s = kt % TG_STAGES;
-                if (!tg_mbar_wait(&ctl->full[s], (kt / TG_STAGES) & 1, abort)) {
+            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++local) {
+                const int buf = local & 1;       // two accumulators: the epilogue drains one while the other fills
+                if (!tg_mbar_wait(&ctl->acc_empty[buf], ((local >> 1) & 1) ^ 1, abort)) {
                     if (!*abort) { *abort = 1; atomicExch(error_flag, TG_ERR_MMA); }
-                    ok = false;
                     break;
                 }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t a_addr = tg_smem(a_tiles + s * TG_A_BYTES), b_addr = tg_smem(b_tiles + s * TG_B_BYTES);
+                const uint32_t acc = tmem + buf * TG_BN;
+                for (int kt = 0; kt < k_tiles; ++kt, ++it) {
+                    const int s = it % TG_STAGES;
+                    if (!tg_mbar_wait(&ctl->full[s], (it / TG_STAGES) & 1, abort)) {
+                        if (!*abort) { *abort = 1; atomicExch(error_flag, TG_ERR_MMA); }
+                        ok = false;
+                        break;
+                    }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t a_addr = tg_smem(a_tiles + s * TG_A_BYTES), b_addr = tg_smem(b_tiles + s * TG_B_BYTES);
 #pragma unroll
-                for (int k = 0; k < TG_BK / 16; ++k)     // 16 elements = 32 bytes further along K inside the swizzled row
-                    tg_mma(tmem, tg_smem_desc(a_addr + k * 32), tg_smem_desc(b_addr + k * 32), idesc, (kt | k) != 0);
-                tg_commit(&ctl->empty[s]);               // arrives when these products have read the stage
+                    for (int k = 0; k < TG_BK / 16; ++k)     // 16 elements = 32 bytes further along K inside the swizzled row
+                        tg_mma(acc, tg_smem_desc(a_addr + k * 32), tg_smem_desc(b_addr + k * 32), idesc, (kt | k) != 0);
+                    tg_commit(&ctl->empty[s]);               // arrives when these products have read the stage
+                }
+                if (ok) tg_commit(&ctl->acc_full[buf]);      // arrives when every product of the tile is done
             }
-            if (ok) tg_commit(&ctl->accum);              // arrives when every product is done
         }
     } else {
         const int q = warp & 3;                          // a warp reads the 32 lanes of tensor memory of its quarter
-        const bool ready = tg_mbar_wait(&ctl->accum, 0, abort);
-        if (!ready && !*abort) { *abort = 1; atomicExch(error_flag, TG_ERR_EPILOGUE); }
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (ready) {
+        int local = 0;
+        for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++local) {
+            const int buf = local & 1;
+            const bool ready = tg_mbar_wait(&ctl->acc_full[buf], (local >> 1) & 1, abort);
+            if (!ready) {
+                if (!*abort) { *abort = 1; atomicExch(error_flag, TG_ERR_EPILOGUE); }
+                break;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int m0 = (t % m_tiles) * TG_BM, n0 = (t / m_tiles) * TG_BN;
             const int row = m0 + q * 32 + lane;
 #pragma unroll 1
             for (int c = 0; c < TG_BN / 32; ++c) {
                 uint32_t r[32];
-                tg_ld32(tmem + ((uint32_t)(q * 32) << 16) + c * 32, r);
+                tg_ld32(tmem + ((uint32_t)(q * 32) << 16) + buf * TG_BN + c * 32, r);
                 const int col = n0 + c * 32;
                 if (row < M && col < N) {
                     if (OUT_F32) {
@@ -215,6 +242,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                     }
                 }
             }
+            // this warp has drained its part of the accumulator: the MMA lane may overwrite it
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(tg_smem(&ctl->acc_empty[buf])) : "memory");
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -266,8 +297,8 @@ extern "C" int gi_gemm_tcgen05_bf16(const void* x, const void* W, void* out, int
                "gi_gemm_tcgen05_bf16: operands must start on 16 bytes");
     GI_REQUIRE(out_dtype == GI_DTYPE_BF16 || out_dtype == GI_DTYPE_F32, "gi_gemm_tcgen05_bf16: output dtype %d", out_dtype);
     GI_REQUIRE(error_flag != nullptr, "gi_gemm_tcgen05_bf16: an error flag on the device is required");
-    const long long gy = (M + TG_BM - 1) / TG_BM;
-    GI_REQUIRE(gy <= 65535, "gi_gemm_tcgen05_bf16: %d rows in one product is beyond %d", M, 65535 * TG_BM);
+    const long long tiles = (long long)((M + TG_BM - 1) / TG_BM) * ((N + TG_BN - 1) / TG_BN);
+    GI_REQUIRE(tiles < 2147483647LL, "gi_gemm_tcgen05_bf16: too many tiles");
     CUtensorMap map_x, map_w;
     if (int rc = tg_make_map(&map_x, x, M, K, TG_BM)) return rc;
     if (int rc = tg_make_map(&map_w, W, N, K, TG_BN)) return rc;
@@ -280,7 +311,12 @@ extern "C" int gi_gemm_tcgen05_bf16(const void* x, const void* W, void* out, int
         if (e != cudaSuccess) { gi_set_error("gi_gemm_tcgen05_bf16: shared memory: %s", cudaGetErrorString(e)); return (int)e; }
         attr_done[f32] = true;
     }
-    dim3 grid((N + TG_BN - 1) / TG_BN, (unsigned)gy);
+    int n_sm = 148;
+    {
+        int dev = 0;
+        if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
+    }
+    dim3 grid((unsigned)(tiles < n_sm ? tiles : n_sm));      // one CTA per SM, each walks its share of the tiles
     if (f32) gi_launch(gemm_tcgen05_kernel<1>, grid, dim3(TG_THREADS), smem, (cudaStream_t)stream, map_x, map_w, out, M, N, K, error_flag);
     else gi_launch(gemm_tcgen05_kernel<0>, grid, dim3(TG_THREADS), smem, (cudaStream_t)stream, map_x, map_w, out, M, N, K, error_flag);
     return gi_check_launch("gi_gemm_tcgen05_bf16");

@@ -1,7 +1,7 @@
 """Single kernels at the benchmark model's sizes, for timing and for profilers.
 
     python -m garlic_inference_b200.ops.microbench run  OP M [SHAPE]     a few plain launches (what ncu captures)
-    python -m garlic_inference_b200.ops.microbench time [linear|attn]    GPU time inside CUDA graphs, cold L2
+    python -m garlic_inference_b200.ops.microbench time [linear|attn|prefill]   GPU time inside CUDA graphs, cold L2
 
 OP: gemv | skinny | cublas (M = rows of x, SHAPE = qkv | o | gate_up | down | lm_head at Qwen3-8B sizes),
 attn_decode (M = sequences, 2,048 cached tokens each), attn_prefill (M = prompt length).
@@ -123,6 +123,21 @@ def time_attention() -> None:
             del pools
 
 
+def time_prefill_linear(m: int = 2048) -> None:
+    """The products of a prompt of `m` tokens: this library's tcgen05 kernel against the library product."""
+    for shape, (n, k) in SHAPES.items():
+        if shape == "lm_head":
+            continue
+        ws = _weights(shape, 3)
+        xs = [torch.randn(m, k, device=DEV, dtype=torch.bfloat16) for _ in range(3)]
+        flops = 2.0 * m * n * k
+        res = {"tcgen05": graph_time([(lambda w=w, x=x: kernels.gemm_tcgen05_bf16(x, w, torch.bfloat16)) for w, x in zip(ws, xs)]),
+               "cublas": graph_time([(lambda w=w, x=x: torch.mm(x, w.t())) for w, x in zip(ws, xs)])}
+        print(f"{shape:8s} M={m}  " + "  ".join(f"{op}: {ms * 1e3:7.1f} us {flops / ms / 1e9:6.0f} TFLOP/s"
+                                                for op, ms in res.items()), flush=True)
+    print("error flag", int(kernels.tcgen05_error_flag(DEV).item()))
+
+
 def main(argv) -> int:
     if len(argv) >= 3 and argv[0] == "run":
         run(argv[1], int(argv[2]), argv[3] if len(argv) > 3 else "gate_up")
@@ -132,6 +147,8 @@ def main(argv) -> int:
             time_linear()
         if which in ("all", "attn"):
             time_attention()
+        if which in ("all", "prefill"):
+            time_prefill_linear()
     else:
         print(__doc__)
         return 2
