@@ -132,6 +132,11 @@ class Engine:
         entries = list(entries)
         if not entries:
             return None
+        if self.graphs is not None and all(len(e.tokens) == 1 and len(e.want) == 1 for e in entries):
+            # the common decode step (one token each, each wanted), without per-entry array work
+            logits = self._decode_fast(entries)
+            if logits is not None:
+                return logits
         (toks, pos, slot, want_rows), (starts, lens, past) = self.describe(entries)
         slots = [e.slot for e in entries]
         self.cache.prepare(slots, lens)                  # raises before anything is launched
@@ -145,20 +150,44 @@ class Engine:
                     return logits
                 return logits[torch.from_numpy(want_rows.astype(np.int64)).to(logits.device)]
         single = all(n == 1 for n in lens)
-        tiles = np.zeros((0, 4), dtype=np.int32) if single else np.asarray(
-            [(s, st + r0, min(64, n - r0), p + r0)
-             for s, st, n, p in zip(slots, starts, lens, past) for r0 in range(0, n, 64)], dtype=np.int32)
+
+        def runs(rows: int) -> np.ndarray:
+            if single:
+                return np.zeros((0, 4), dtype=np.int32)
+            return np.asarray([(s, st + r0, min(rows, n - r0), p + r0)
+                               for s, st, n, p in zip(slots, starts, lens, past) for r0 in range(0, n, rows)],
+                              dtype=np.int32)
+
+        tiles, tiles128 = runs(64), runs(128)
         # the runs go first: the kernels read them 16 bytes at a time
-        d_tiles, d_toks, d_pos, d_slot, d_want = self._staging.upload([tiles.reshape(-1), toks, pos, slot, want_rows])
+        d_tiles, d_tiles128, d_toks, d_pos, d_slot, d_want = self._staging.upload(
+            [tiles.reshape(-1), tiles128.reshape(-1), toks, pos, slot, want_rows])
         ctx = StepContext(
             n_tokens=int(toks.size), tokens=d_toks, tok_pos=d_pos, tok_slot=d_slot,
             q_tiles=None if single else d_tiles.view(-1, 4),
+            q_tiles128=None if single else d_tiles128.view(-1, 4),
             seq_slots=slots, seq_starts=starts, seq_lens=lens, seq_past=past,
             all_single=all(n == 1 for n in lens),
             max_kv_len=max(p + n for p, n in zip(past, lens)),
             status=self.cache.status)
         logits = self.model.forward(ctx, self.cache, d_want if want_rows.size else None)
         self.cache.commit(slots, lens)
+        return logits
+
+    def _decode_fast(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        toks = [int(e.tokens[0]) for e in entries]
+        if min(toks) < 0 or max(toks) >= self.model.vocab_size:
+            bad = next(t for t in toks if t < 0 or t >= self.model.vocab_size)
+            raise StepError(f"token id {bad} is outside the vocabulary of {self.model.vocab_size}")
+        if any(e.want[0] != 0 for e in entries):
+            raise StepError("want index outside the entry's 1 tokens")
+        slots = [e.slot for e in entries]
+        lens = [1] * len(slots)
+        self.cache.prepare(slots, lens)
+        past = [self.cache.length(s) for s in slots]
+        logits = self.graphs.run(slots, past, np.asarray(toks, dtype=np.int32), None)
+        if logits is not None:
+            self.cache.commit(slots, lens)
         return logits
 
     def step_decode_device(self, slots: Sequence[int], tokens: torch.Tensor) -> torch.Tensor:
@@ -195,5 +224,14 @@ class Engine:
         return self._staging.bytes_uploaded + (self.graphs.bytes_uploaded if self.graphs else 0)
 
     def check(self) -> None:
-        """Raise if a kernel of an earlier step met an index outside the cache (synchronises)."""
+        """Raise if a kernel of an earlier step met an index outside the cache, or gave up a wait
+        (synchronises)."""
         self.cache.check_status()
+        if self.rt.device.type == "cuda":
+            from ..ops import kernels
+            flag = kernels.tcgen05_error_flag(self.rt.device)
+            code = int(flag.item())
+            if code:
+                flag.zero_()
+                raise RuntimeError(f"a tcgen05 kernel gave up a bounded wait (code {code}: 11-13 product, "
+                                   "21-23 attention, 24 unmapped page)")

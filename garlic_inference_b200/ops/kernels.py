@@ -303,6 +303,33 @@ def attention_prefill_bf16(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.
     return out
 
 
+def tcgen05_attention_takes(dtype: torch.dtype, head_dim: int, page_size: int) -> bool:
+    """Whether the tcgen05 prefill attention takes this element type, head size and page size."""
+    return dtype == torch.bfloat16 and head_dim == 128 and page_size % 64 == 0
+
+
+def attention_prefill_tcgen05(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: torch.Tensor,
+                              q_tiles128: torch.Tensor, scale: float, window: int) -> torch.Tensor:
+    """Flash attention of q [n, n_q, 128] over the paged cache on tcgen05 tensor cores (TMA-fed, S, P and
+    P V in tensor memory).  `q_tiles128` int32 [n_tiles, 4] cuts the rows into runs of at most 128
+    consecutive tokens of one sequence: {slot, first row, rows, position of the first row}."""
+    l = require_gpu()
+    _dense(q, "q", torch.bfloat16), _dense(k_pool, "k_pool", torch.bfloat16), _dense(v_pool, "v_pool", torch.bfloat16)
+    _dense(block_table, "block_table", torch.int32), _dense(q_tiles128, "q_tiles128", torch.int32)
+    n, n_q, d = q.shape
+    n_pages, n_kv, page_size, pool_d = k_pool.shape
+    if pool_d != d or v_pool.shape != k_pool.shape:
+        raise KernelError(f"cache pools {tuple(k_pool.shape)} do not fit head_dim {d}")
+    if q_tiles128.dim() != 2 or q_tiles128.shape[1] != 4 or q_tiles128.data_ptr() % 16:
+        raise KernelError("q_tiles128 must be int32 [n_tiles, 4] starting on 16 bytes")
+    out = torch.zeros((n, n_q * d), dtype=q.dtype, device=q.device)       # rows in no tile (padding) stay zero
+    check(l.gi_attention_prefill_tcgen05(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_table), _ptr(q_tiles128),
+                                         q_tiles128.shape[0], _ptr(out), n, n_q, n_kv, d, page_size,
+                                         block_table.shape[1], n_pages, int(window or 0), float(scale),
+                                         _ptr(tcgen05_error_flag(q.device)), _stream()), l)
+    return out
+
+
 def decode_splits(n_seqs: int, n_kv: int) -> int:
     """Slices of the keys per (sequence, key/value head) in the decode kernel.  Measured on a B200:
     about 256 CTAs are wanted at small batches (but at most 16 slices), and two slices still pay

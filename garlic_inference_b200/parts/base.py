@@ -75,6 +75,7 @@ class StepContext:
     # the rows cut into runs of at most 64 consecutive tokens of one sequence, int32 [n_runs, 4] =
     # {slot, first row, rows, position of the first row}; None in decode steps
     q_tiles: Optional[torch.Tensor] = None
+    q_tiles128: Optional[torch.Tensor] = None          # the same cut into runs of at most 128 rows
     status: Optional[torch.Tensor] = None   # int32[1] error flag shared with the cache
     captured: bool = False              # the step is being recorded into a CUDA graph: the host-side
                                         # lists above are empty, everything must come from the tensors

@@ -472,6 +472,61 @@ def test_attention_decode_bf16(n_q, n_kv, d, page, window, splits):
         torch.testing.assert_close(out[i], ref, rtol=2e-2, atol=2e-2, msg=lambda msg: f"seq {s}: {msg}")
 
 
+def _tiles128_for(runs):
+    out = []
+    for slot, row0, n, pos0 in runs:
+        for r0 in range(0, n, 128):
+            out.append((slot, row0 + r0, min(128, n - r0), pos0 + r0))
+    return torch.tensor(out, dtype=torch.int32, device=DEV)
+
+
+@pytest.mark.parametrize("n_q,n_kv,page,window", [(4, 4, 64, 0), (8, 2, 64, 0), (5, 1, 128, 0), (4, 2, 64, 70),
+                                                  (2, 1, 128, 200), (32, 8, 64, 0)])
+def test_attention_prefill_tcgen05(n_q, n_kv, page, window):
+    d = 128
+    lens = [1, 37, 300, 64, 65, 130, 513]
+    new = [1, 37, 250, 64, 3, 129, 513]        # the last `new` positions of each sequence are this step's queries
+    k_pool, v_pool, bt, kd, vd = make_cache(len(lens), lens, n_kv, d, page, torch.bfloat16, seed=page + n_q)
+    runs, row = [], 0
+    for s, (n, m) in enumerate(zip(lens, new)):
+        runs.append((s, row, m, n - m))
+        row += m
+    row += 2                                   # two padding rows at the end, in no tile
+    g = torch.Generator(device=DEV).manual_seed(19)
+    q = torch.randn(row, n_q, d, generator=g, device=DEV).to(torch.bfloat16)
+    scale = d ** -0.5
+    flag = K().tcgen05_error_flag(q.device)
+    flag.zero_()
+    out = K().attention_prefill_tcgen05(q, k_pool, v_pool, bt, _tiles128_for(runs), scale, window).float().view(row, n_q, d)
+    torch.cuda.synchronize()
+    assert int(flag.item()) == 0, "a bounded wait of the kernel ran out"
+    assert float(out[-2:].abs().sum()) == 0
+    for s, row0, m, pos0 in runs:
+        for i in range(0, m, 7 if m > 100 else 1):
+            ref = ref_attention(q[row0 + i].float(), kd[s], vd[s], pos0 + i, scale, window).float()
+            torch.testing.assert_close(out[row0 + i], ref, rtol=2e-2, atol=2e-2,
+                                       msg=lambda msg: f"seq {s} position {pos0 + i}: {msg}")
+
+
+def test_attention_prefill_tcgen05_finds_one_far_key():
+    n_q, n_kv, d, page, n = 4, 2, 128, 64, 700
+    for far in (0, 1, 63, 64, 127, 128, 333, 639, 640, 698, 699):
+        k_pool, v_pool, bt, kd, vd = make_cache(1, [n], n_kv, d, page, torch.bfloat16, seed=far + 3)
+        q = torch.zeros(1, n_q, d, device=DEV)
+        for h in range(n_q):
+            q[0, h] = kd[0][far, h // 2] * 2.0
+        q = q.to(torch.bfloat16)
+        tiles = _tiles128_for([(0, 0, 1, n - 1)])
+        out = K().attention_prefill_tcgen05(q, k_pool, v_pool, bt, tiles, 1.0, 0).float().view(n_q, d)
+        for h in range(n_q):
+            torch.testing.assert_close(out[h], vd[0][far, h // 2], rtol=2e-2, atol=2e-2,
+                                       msg=lambda msg: f"far key {far}, head {h}: {msg}")
+        if far < n - 40:
+            gone = K().attention_prefill_tcgen05(q, k_pool, v_pool, bt, tiles, 1.0, n - 1 - far).float().view(n_q, d)
+            assert float((gone[0] - vd[0][far, 0]).abs().max()) > 0.1, "the window's edge lets it in"
+    assert int(K().tcgen05_error_flag(q.device).item()) == 0
+
+
 @pytest.mark.parametrize("kernel", ["decode", "prefill"])
 def test_tensor_core_attention_finds_one_far_key(kernel):
     n_q, n_kv, d, page, n = 8, 2, 64, 16, 700

@@ -14,7 +14,9 @@ LENGTHS = {
     "A": [7, 128, 33, 64, 1, 65, 100],
     "B": [5, 11, 2, 300, 97, 64, 129],
     "C": [90, 41, 40, 200, 17, 3, 130],
+    "D": [300, 64, 1, 129, 700, 65, 128],
 }
+PAGE = {"A": 16, "B": 16, "C": 16, "D": 64}
 BATCHES = [["r0", "r1", "r2"], ["r3", "r4"], ["r5", "r6"]]
 
 
@@ -37,13 +39,13 @@ def plain_cache(model_dirs):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_every_cutting_agrees_with_the_plain_implementation(name, dtype, gpu_models, plain_cache):
     reqs, want = plain_cache(name)
     tol = tiny.TOL[dtype]
     # a cache that holds the largest batch and no more: later batches must reuse slots and pages
     max_tokens = max(sum(_round64(len(reqs[r])) for r in b) for b in BATCHES)
-    model = gpu_models(name, dtype, max_tokens=max_tokens, page_size=16)
+    model = gpu_models(name, dtype, max_tokens=max_tokens, page_size=PAGE[name])
 
     whole = tiny.run_trace_in_process(model, tiny.trace_whole(reqs))
     tiny.assert_covers(whole, reqs)

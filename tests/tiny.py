@@ -1,6 +1,6 @@
 """Tiny configurations, traces and comparison helpers shared by the tests.
 
-Three configurations of the architecture that differ in every size and option:
+Configurations of the architecture that differ in every size and option:
 layers, width (one no power of two), heads and groups (2, 6 and 1 query heads
 per key/value head), head sizes 16 / 32 / 48, feed-forward width, vocabulary,
 rope theta, the norms' eps, positions, tied or separate head, and the window
@@ -34,6 +34,11 @@ TINY = {
                        layer_types=["full_attention", "sliding_attention", "sliding_attention",
                                     "full_attention"]),
               seed=2, std=0.08, norm_std=0.15),
+    # heads of 128 (and, in the tests, cache pages of 64): the sizes the tcgen05 attention kernel takes
+    "D": dict(cfg=dict(hidden_size=256, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                       head_dim=128, intermediate_size=320, vocab_size=600, rope_theta=1e6, rms_norm_eps=1e-6,
+                       max_position_embeddings=1024, tie_word_embeddings=False),
+              seed=3, std=0.04, norm_std=0.1),
 }
 
 # tolerances (never widened to pass): float32 logits against the plain float32 implementation,
