@@ -26,14 +26,18 @@ extern "C" const char* gi_last_error(void) { return g_error; }
 
 #include <stdlib.h>
 #include <string.h>
+// GARLIC_B200_PDL=0 or =1 in the environment decides for the whole process; otherwise the caller's last
+// gi_set_pdl() does (off until then).
+static int g_pdl_requested = 0;
 bool gi_pdl_enabled() {
-    static int enabled = -1;
-    if (enabled < 0) {
+    static int from_env = -2;
+    if (from_env == -2) {
         const char* v = getenv("GARLIC_B200_PDL");
-        enabled = (v && strcmp(v, "1") == 0) ? 1 : 0;
+        from_env = (v && strcmp(v, "1") == 0) ? 1 : (v && strcmp(v, "0") == 0) ? 0 : -1;
     }
-    return enabled == 1;
+    return from_env >= 0 ? from_env == 1 : g_pdl_requested == 1;
 }
+extern "C" void gi_set_pdl(int on) { g_pdl_requested = on ? 1 : 0; }
 
 // Compute capability of the current device as major*10+minor, or a negative CUDA error.
 extern "C" int gi_device_arch(void) {

@@ -41,15 +41,24 @@ typedef __nv_bfloat16 bf16;
 // launches carry the attribute below, it lets the next kernel of the stream be launched while this one
 // still runs (its blocks then sit in their own gi_pdl_start until this grid has finished and its writes
 // are visible).  Nothing may be read or written before it.  Without the attribute both instructions do
-// nothing.  Measured on a B200 inside the recorded decode step it did not pay (batch 1: 4.6 ms a step
-// with it, 3.9 ms without), so it is off unless GARLIC_B200_PDL=1 is set in the environment.
+// nothing.  Measured on a B200 inside the recorded decode step of Qwen3-8B sizes, with the products
+// fetching their first weights before the wait: batch 8 +1 to 4 %, batch 64 +1 %, batch 1 -2 %.  So the
+// engine asks for it (gi_set_pdl) while it records steps of two and more sequences, and nowhere else;
+// GARLIC_B200_PDL=0 or =1 in the environment overrides that for the whole process.
 __device__ __forceinline__ void gi_pdl_start() {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
 }
+// The two halves apart, for kernels that have something to do that depends on no earlier kernel (fetching
+// weights): gi_pdl_launch_dependents() first, then that work, then gi_pdl_wait() before anything an
+// earlier kernel wrote is read and before anything is written.
+__device__ __forceinline__ void gi_pdl_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void gi_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 // kernel<<<grid, block, smem, stream>>>(args...), with the attribute that allows the overlap above when
-// GARLIC_B200_PDL=1.
+// gi_pdl_enabled().
 bool gi_pdl_enabled();
 template <typename... KArgs, typename... Args>
 static inline void gi_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,

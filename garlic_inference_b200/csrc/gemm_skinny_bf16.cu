@@ -65,7 +65,7 @@ __global__ void __launch_bounds__(SK_THREADS)
 skinny_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, void* __restrict__ out, int out_f32,
                    int M, int N, int K, int k_slice) {
     static_assert(WR * WK == SK_WARPS, "8 warps");
-    gi_pdl_start();
+    gi_pdl_launch_dependents();
     constexpr int MP = 8 * NT;                   // padded batch
     constexpr int R = 16 * WR;                   // W rows per CTA
     constexpr int CH = 4;                        // 16-byte pieces of W a thread brings in per chunk
@@ -129,6 +129,7 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, void*
     };
 #pragma unroll
     for (int i = 0; i < SK_DEPTH - 1; ++i) issue(i);
+    gi_pdl_wait();                               // W is nobody's output: its first chunks are on their way by now
     uint4 x0[NT], x1[NT];
     load_x(0, x0, x1);
     for (int i = 0; i < n_chunks; ++i) {

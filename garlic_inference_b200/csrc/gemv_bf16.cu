@@ -38,7 +38,7 @@ __device__ __forceinline__ void fma8(const uint4& w, const bf16* __restrict__ x,
 template <int M, typename OutT>
 __global__ void __launch_bounds__(GV_WARPS * 32)
 gemv_bf16_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, OutT* __restrict__ out, int N, int K) {
-    gi_pdl_start();
+    gi_pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n = blockIdx.x * GV_WARPS + warp;
     if (n >= N) return;
@@ -48,6 +48,21 @@ gemv_bf16_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, OutT* _
 #pragma unroll
     for (int m = 0; m < M; ++m) acc[m] = 0.f;
     int v = lane;
+    // W is nobody's output: the first loads go out before the wait for the kernel that makes x
+    const bool head = v + 96 < nvec;
+    uint4 h0, h1, h2, h3;
+    if (head) {
+        h0 = ld_stream(wrow + v), h1 = ld_stream(wrow + v + 32);
+        h2 = ld_stream(wrow + v + 64), h3 = ld_stream(wrow + v + 96);
+    }
+    gi_pdl_wait();
+    if (head) {
+        fma8<M>(h0, x, K, v * 8, acc);
+        fma8<M>(h1, x, K, (v + 32) * 8, acc);
+        fma8<M>(h2, x, K, (v + 64) * 8, acc);
+        fma8<M>(h3, x, K, (v + 96) * 8, acc);
+        v += 128;
+    }
     for (; v + 96 < nvec; v += 128) {
         const uint4 w0 = ld_stream(wrow + v), w1 = ld_stream(wrow + v + 32);
         const uint4 w2 = ld_stream(wrow + v + 64), w3 = ld_stream(wrow + v + 96);

@@ -20,7 +20,7 @@ from typing import Optional
 import numpy as np
 import torch
 
-from ..ops import counters
+from ..ops import counters, kernels
 from ..parts import StepContext
 
 
@@ -78,8 +78,14 @@ class DecodeGraphs:
         if self._pool is None:
             self._pool = torch.cuda.graph_pool_handle()
         before = counters.launches
-        with torch.cuda.graph(cap.graph, pool=self._pool):
-            cap.logits = self.model.forward(ctx, self.cache, cap.want)
+        # recorded steps of two and more sequences let each kernel be launched while the one before it
+        # still runs (measured: a gain there, a small loss for one sequence)
+        kernels.set_dependent_launch(size >= 2)
+        try:
+            with torch.cuda.graph(cap.graph, pool=self._pool):
+                cap.logits = self.model.forward(ctx, self.cache, cap.want)
+        finally:
+            kernels.set_dependent_launch(False)
         cap.n_kernels = counters.launches - before
         counters.launches = before                        # capturing launches nothing
         return cap

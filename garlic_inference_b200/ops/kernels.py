@@ -43,6 +43,12 @@ def _ptr(t: Optional[torch.Tensor]):
     return None if t is None else t.data_ptr()
 
 
+def set_dependent_launch(on: bool) -> None:
+    """Whether the launches that follow carry the attribute for programmatic dependent launch (the next
+    kernel may be launched, and fetch its weights, while this one still runs)."""
+    require_gpu().gi_set_pdl(1 if on else 0)
+
+
 def embedding(ids: torch.Tensor, table: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """float32 rows of `table` for int32 `ids`: the start of the residual stream."""
     l = require_gpu()

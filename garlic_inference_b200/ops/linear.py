@@ -8,17 +8,25 @@ Which product runs:
   * bfloat16 weight, 2 to 8 rows: this package's tensor-core kernel for
     decode batches, which reads the weight once.
   * bfloat16 weight, more rows: the library product (cuBLAS through
-    `torch.mm`), float32 accumulation.  Upstream uses the same library for all
+    `torch.mm`), float32 accumulation, or this package's tcgen05 kernel when
+    `LARGE_GEMM` says so.  Upstream uses the same library for all
     its products (src/src-cuda/mat-ops/gemm/gemm.cu:22-41).
 """
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import torch
 
 from . import kernels
 from .library import KernelError
+
+# Which product takes bfloat16 weights with more than SKINNY_MAX_ROWS rows of x: "library" (cuBLAS through
+# torch.mm) or "tcgen05" (this package's TMA/tcgen05 kernel).  Measured at 2,048 rows and Qwen3-8B sizes the
+# library runs 1.43-1.53 PFLOP/s and the tcgen05 kernel 1.09-1.27, so the library is the default; set
+# GARLIC_B200_GEMM=tcgen05 (or this variable) to run this package's kernel instead.
+LARGE_GEMM = os.environ.get("GARLIC_B200_GEMM", "library")
 
 GEMV_MAX_ROWS = 1          # one row: the plain bandwidth kernel
 SKINNY_MAX_ROWS = 8        # up to here: the tensor-core kernel that streams W once (it takes 16; the library is faster from 9 on)
@@ -43,6 +51,8 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
             return kernels.gemv_bf16(x, w, out_dtype)
         return kernels.gemm_skinny_bf16(x, w, out_dtype)
     kernels.require_gpu()
+    if LARGE_GEMM == "tcgen05" and k % 8 == 0 and w.data_ptr() % 16 == 0 and x.data_ptr() % 16 == 0:
+        return kernels.gemm_tcgen05_bf16(x, w, out_dtype)
     if out_dtype == torch.float32:
         return torch.mm(x, w.t(), out_dtype=torch.float32)
     return torch.mm(x, w.t())

@@ -135,6 +135,19 @@ def time_prefill_linear(m: int = 2048) -> None:
                "cublas": graph_time([(lambda w=w, x=x: torch.mm(x, w.t())) for w, x in zip(ws, xs)])}
         print(f"{shape:8s} M={m}  " + "  ".join(f"{op}: {ms * 1e3:7.1f} us {flops / ms / 1e9:6.0f} TFLOP/s"
                                                 for op, ms in res.items()), flush=True)
+    # causal attention of the same prompt: 4 * n_q * d * m^2 / 2 flops
+    n_pages = -(-m // PAGE)
+    k_pool = torch.randn(n_pages, N_KV, PAGE, HEAD_DIM, device=DEV, dtype=torch.bfloat16)
+    v_pool = torch.randn_like(k_pool)
+    table = torch.arange(n_pages, dtype=torch.int32, device=DEV).view(1, -1)
+    q = torch.randn(m, N_Q, HEAD_DIM, device=DEV, dtype=torch.bfloat16)
+    t64 = torch.tensor([(0, r, min(64, m - r), r) for r in range(0, m, 64)], dtype=torch.int32, device=DEV)
+    t128 = torch.tensor([(0, r, min(128, m - r), r) for r in range(0, m, 128)], dtype=torch.int32, device=DEV)
+    flops = 4.0 * N_Q * HEAD_DIM * m * (m + 1) / 2
+    res = {"tcgen05": graph_time([lambda: kernels.attention_prefill_tcgen05(q, k_pool, v_pool, table, t128, HEAD_DIM ** -0.5, 0)] * 3),
+           "mma.sync": graph_time([lambda: kernels.attention_prefill_bf16(q, k_pool, v_pool, table, t64, HEAD_DIM ** -0.5, 0)] * 3)}
+    print(f"attention M={m}  " + "  ".join(f"{op}: {ms * 1e3:7.1f} us {flops / ms / 1e9:6.0f} TFLOP/s" for op, ms in res.items()),
+          flush=True)
     print("error flag", int(kernels.tcgen05_error_flag(DEV).item()))
 
 

@@ -184,3 +184,17 @@ def test_step_errors_come_before_any_launch(gpu_models):
         assert out.shape == (1, 512) and out.dtype == torch.float32
     finally:
         model.free_slot(s)
+
+
+def test_tcgen05_products_in_the_model(model_dirs, plain_cache, monkeypatch):
+    """The same cuttings with this package's tcgen05 kernel taking every product of more than 8 rows
+    (the library product is the default there)."""
+    from garlic_inference_b200 import AutoModel
+    import sys
+    monkeypatch.setattr(sys.modules["garlic_inference_b200.ops.linear"], "LARGE_GEMM", "tcgen05")
+    reqs, want = plain_cache("D")
+    model = AutoModel.from_pretrained(model_dirs("D"), device=0, dtype="bfloat16", max_tokens=2048, page_size=64)
+    for steps in (tiny.trace_whole(reqs), tiny.trace_batched(reqs, BATCHES, prompt_frac=0.5)):
+        got = tiny.run_trace_in_process(model, steps)
+        tiny.assert_covers(got, reqs)
+        tiny.compare(got, want, tiny.TOL["bfloat16"], "D bfloat16 with tcgen05 products")
