@@ -1,7 +1,7 @@
 """Single kernels at the benchmark model's sizes, for timing and for profilers.
 
     python -m garlic_inference_b200.ops.microbench run  OP M [SHAPE]     a few plain launches (what ncu captures)
-    python -m garlic_inference_b200.ops.microbench time [linear|attn|prefill]   GPU time inside CUDA graphs, cold L2
+    python -m garlic_inference_b200.ops.microbench time [linear|attn|prefill|small]   GPU time inside CUDA graphs, cold L2
 
 OP: gemv | skinny | cublas (M = rows of x, SHAPE = qkv | o | gate_up | down | lm_head at Qwen3-8B sizes),
 attn_decode (M = sequences, 2,048 cached tokens each), attn_prefill (M = prompt length).
@@ -123,6 +123,31 @@ def time_attention() -> None:
             del pools
 
 
+def time_small(hidden: int = 4096, inter: int = 12288) -> None:
+    """The kernels between the products of a decode step, 32 calls back to back in a graph on operands
+    that stay in L2 (as they do in a step, where the kernel before has just written them)."""
+    for m in (1, 8, 64):
+        res = torch.randn(m, hidden, device=DEV)
+        delta = torch.randn(m, hidden, device=DEV, dtype=torch.bfloat16)
+        w = torch.ones(hidden, device=DEV, dtype=torch.bfloat16)
+        gate_up = torch.randn(m, 2 * inter, device=DEV, dtype=torch.bfloat16)
+        qkv = torch.randn(m, (N_Q + 2 * N_KV) * HEAD_DIM, device=DEV, dtype=torch.bfloat16)
+        wn = torch.ones(HEAD_DIM, device=DEV, dtype=torch.bfloat16)
+        ctx = 2048
+        pools, table, _, pos, slot = _decode_case(m, ctx, 1)
+        cos = torch.randn(ctx, HEAD_DIM // 2, device=DEV)
+        sin = torch.randn(ctx, HEAD_DIM // 2, device=DEV)
+        status = torch.zeros(1, dtype=torch.int32, device=DEV)
+        times = {
+            "add_rmsnorm": graph_time([lambda: kernels.add_rmsnorm(delta, res, w, 1e-6, torch.bfloat16)] * 32),
+            "swiglu": graph_time([lambda: kernels.swiglu(gate_up)] * 32),
+            "qk_norm_rope_append": graph_time([lambda: kernels.qk_norm_rope_append(
+                qkv, N_Q, N_KV, HEAD_DIM, wn, wn, 1e-6, cos, sin, HEAD_DIM, pos, slot, pools[0][0], pools[0][1], table,
+                status)] * 32),
+        }
+        print(f"M={m:3d}  " + "  ".join(f"{k}: {v * 1e3:5.2f} us" for k, v in times.items()), flush=True)
+
+
 def time_prefill_linear(m: int = 2048) -> None:
     """The products of a prompt of `m` tokens: this library's tcgen05 kernel against the library product."""
     for shape, (n, k) in SHAPES.items():
@@ -162,6 +187,8 @@ def main(argv) -> int:
             time_attention()
         if which in ("all", "prefill"):
             time_prefill_linear()
+        if which in ("all", "small"):
+            time_small()
     else:
         print(__doc__)
         return 2
