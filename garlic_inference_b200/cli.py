@@ -25,9 +25,15 @@ def parse_ids(text: str) -> list[int]:
 
 def build_parser() -> argparse.ArgumentParser:
     ap = argparse.ArgumentParser(prog="runner", description="generate token ids with a model folder on one B200")
-    ap.add_argument("model_dir", metavar="MODEL_DIR", help="folder with config.json and model.safetensors")
+    ap.add_argument("model_dir", metavar="MODEL_DIR",
+                    help="folder with config.json and model.safetensors (with --random-weights: a config.json "
+                         "or a folder that holds one; no weights are read)")
     ap.add_argument("--prompt-ids", action="append", default=None,
                     help="a prompt as token ids '1,2,3' (repeat for a batch); default: read prompts from stdin")
+    ap.add_argument("--prompt-file", default=None, help="a file with one prompt (token ids) per line")
+    ap.add_argument("--random-weights", action="store_true",
+                    help="random weights of the configuration's sizes, made on the device")
+    ap.add_argument("--weights-seed", type=int, default=0, help="seed of --random-weights")
     ap.add_argument("--max-new-tokens", type=int, default=600, help="tokens to generate per prompt (upstream: 600)")
     ap.add_argument("--temperature", type=float, default=0.0, help="0 = greedy (upstream's only mode)")
     ap.add_argument("--seed", type=int, default=0, help="seed of temperature sampling")
@@ -44,8 +50,11 @@ def build_parser() -> argparse.ArgumentParser:
 
 def main(argv=None) -> int:
     args = build_parser().parse_args(argv)
-    if args.prompt_ids:
-        prompts = [parse_ids(p) for p in args.prompt_ids]
+    if args.prompt_ids or args.prompt_file:
+        prompts = [parse_ids(p) for p in args.prompt_ids or []]
+        if args.prompt_file:
+            with open(args.prompt_file) as f:
+                prompts += [parse_ids(line) for line in f if line.strip()]
     else:
         if sys.stdin.isatty():
             print("Ask the model something (token ids): ", end="", flush=True)
@@ -61,8 +70,12 @@ def main(argv=None) -> int:
     from .config import load_config
     max_pos = load_config(args.model_dir).max_position_embeddings
     need = sum(tokens_held(len(p), args.max_new_tokens, max_pos) for p in prompts[:args.max_batch or len(prompts)])
-    model = AutoModel.from_pretrained(args.model_dir, device=args.device, dtype=args.dtype,
-                                      max_tokens=args.max_tokens or need, page_size=args.page_size)
+    if args.random_weights:
+        model = AutoModel.from_random(load_config(args.model_dir), seed=args.weights_seed, device=args.device,
+                                      dtype=args.dtype, max_tokens=args.max_tokens or need, page_size=args.page_size)
+    else:
+        model = AutoModel.from_pretrained(args.model_dir, device=args.device, dtype=args.dtype,
+                                          max_tokens=args.max_tokens or need, page_size=args.page_size)
     stop = None if args.stop_ids is None else parse_ids(args.stop_ids)
     out = model.generate(prompts, max_new_tokens=args.max_new_tokens, temperature=args.temperature,
                          seed=args.seed, stop_token_ids=stop, max_batch=args.max_batch)

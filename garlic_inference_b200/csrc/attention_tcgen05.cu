@@ -2,19 +2,21 @@
 // that are a multiple of 64 tokens.
 //
 // One CTA takes 128 consecutive queries of one sequence and one query head, and walks the keys of the
-// sequence's cache 64 at a time:
+// sequence's cache 64 at a time; two CTAs share an SM, so that one's softmax runs under the other's products:
 //   warp 0, one lane:  TMA.  The query tile once; per key tile the 64 keys and 64 values of the tile's
 //                      page (the pools are 2-D tensor maps [all rows, head_dim]; a tile never crosses a
-//                      page), into one of three shared-memory stages, 128-byte swizzled.
-//   warp 1, one lane:  MMA.  S = Q K^T (128 x 64, float32) into tensor memory; when the softmax warps
-//                      have written the probabilities back to tensor memory as bfloat16, P V (128 x 128)
-//                      with P read from tensor memory and V from shared memory.
+//                      page), into rings of two stages each for keys and for values, 128-byte swizzled.
+//   warp 1, one lane:  MMA.  S = Q K^T (128 x 64, float32) into one of two buffers in tensor memory, one
+//                      tile ahead of the softmax; when the softmax warps have written the probabilities
+//                      over the scores as bfloat16, O += P V (128 x 128) with P read from tensor memory
+//                      and V from shared memory.  O stays in tensor memory for all tiles.
 //   warps 2..5:        softmax.  Thread i owns query row i: it reads its row of S from tensor memory,
-//                      scales and masks it (causal, window), keeps the running maximum and sum, writes
-//                      the probabilities, and adds the tile's P V, read from tensor memory, into its 128
-//                      output registers after rescaling them.  No shuffles, no shared memory.
-// The next tile's Q K^T is issued as soon as the probabilities of this tile are in, so it runs while the
-// softmax warps fold P V into their registers.
+//                      scales and masks it (causal, window), and writes exp2(s - ref).  `ref` follows
+//                      the row's running maximum lazily: only when the maximum has grown by more than
+//                      FT_LAZY (in powers of two) are ref, the running sum and the row of O in tensor
+//                      memory rescaled; until then probabilities up to 2^FT_LAZY are simply accumulated,
+//                      which float32 holds exactly as well.  No shuffles, no shared memory, and O is
+//                      read once, at the end.
 //
 // Scores, softmax and the output sum are float32; probabilities are rounded to bfloat16 for the second
 // product.  Every wait on an mbarrier is bounded: when one runs out, a code goes to *error_flag, all
@@ -30,14 +32,15 @@
 #define FT_BM 128
 #define FT_BN 64
 #define FT_D 128
-#define FT_STAGES 3
+#define FT_STAGES 2
 #define FT_THREADS 192
 #define FT_Q_BYTES (FT_BM * FT_D * 2)          // two 128 x 64 swizzled halves
 #define FT_KV_BYTES (FT_BN * FT_D * 2)         // two 64 x 64 swizzled halves, keys; the same for values
 #define FT_TMEM_COLS 256
-#define FT_COL_S 0                             // S: 64 float32 columns
-#define FT_COL_P 64                            // P: 64 bfloat16 = 32 columns
-#define FT_COL_O 128                           // P V of the tile: 128 float32 columns
+#define FT_COL_S 0                             // S: two buffers of 64 float32 columns; P (64 bfloat16 = 32 columns)
+                                               // overwrites the start of its S
+#define FT_COL_O 128                           // O: 128 float32 columns
+#define FT_LAZY 8.f                            // growth of a row's maximum (log2) that triggers a rescale
 #define FT_SPIN_LIMIT (1 << 22)
 
 #define FT_ERR_PRODUCER 21
@@ -47,11 +50,11 @@
 
 struct FtControl {
     unsigned long long q_full;
-    unsigned long long kv_full[FT_STAGES];
-    unsigned long long kv_empty[FT_STAGES];
-    unsigned long long s_full;
-    unsigned long long p_ready;
-    unsigned long long o_full;
+    unsigned long long k_full[FT_STAGES], k_empty[FT_STAGES];
+    unsigned long long v_full[FT_STAGES], v_empty[FT_STAGES];
+    unsigned long long s_full[2];
+    unsigned long long p_ready[2];
+    unsigned long long o_done;
     unsigned int tmem_base;
     int abort;
 };
@@ -109,6 +112,11 @@ __device__ __forceinline__ void ft_mma_ts(uint32_t tmem_d, uint32_t tmem_a, uint
 __device__ __forceinline__ void ft_commit(void* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(ft_smem(bar)) : "memory");
 }
+__device__ __forceinline__ float ft_ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ void ft_ld32(uint32_t taddr, float (&r)[32]) {
     uint32_t u[32];
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
@@ -136,7 +144,7 @@ __device__ __forceinline__ void ft_st32(uint32_t taddr, const uint32_t (&u)[32])
 }
 
 // tiles[t] = {slot, first row of q, rows in the tile (<= 128), position of the first row}
-__global__ void __launch_bounds__(FT_THREADS, 1)
+__global__ void __launch_bounds__(FT_THREADS, 2)
 flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                              const __grid_constant__ CUtensorMap map_v, const int* __restrict__ block_table,
                              const int4* __restrict__ tiles, bf16* __restrict__ out, int n_q, int n_kv,
@@ -162,10 +170,12 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __
 
     if (threadIdx.x == 0) {
         ft_mbar_init(&ctl->q_full, 1);
-        for (int s = 0; s < FT_STAGES; ++s) { ft_mbar_init(&ctl->kv_full[s], 1); ft_mbar_init(&ctl->kv_empty[s], 1); }
-        ft_mbar_init(&ctl->s_full, 1);
-        ft_mbar_init(&ctl->p_ready, 4);
-        ft_mbar_init(&ctl->o_full, 1);
+        for (int s = 0; s < FT_STAGES; ++s) {
+            ft_mbar_init(&ctl->k_full[s], 1); ft_mbar_init(&ctl->k_empty[s], 1);
+            ft_mbar_init(&ctl->v_full[s], 1); ft_mbar_init(&ctl->v_empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) { ft_mbar_init(&ctl->s_full[b], 1); ft_mbar_init(&ctl->p_ready[b], 4); }
+        ft_mbar_init(&ctl->o_done, 1);
         ctl->abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -185,30 +195,43 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __
             ft_tma_load_2d(q_tile, &map_q, h * FT_D, row0, &ctl->q_full);
             ft_tma_load_2d(q_tile + FT_Q_BYTES / 2, &map_q, h * FT_D + 64, row0, &ctl->q_full);
             const int* bt_row = block_table + (size_t)slot * max_pages;
-            int armed = 0;
-            for (int it = 0; it < n_tiles; ++it) {
-                const int s = it % FT_STAGES;
-                if (!ft_mbar_wait(&ctl->kv_empty[s], ((it / FT_STAGES) & 1) ^ 1, abort)) {
-                    if (!*abort) { *abort = 1; atomicExch(error_flag, FT_ERR_PRODUCER); }
-                    break;
-                }
+            // Keys and values have rings of their own: the keys of a tile are free again as soon as its
+            // scores are computed (a tile ahead of the softmax), the values only after P V.  Keys of tile
+            // it + 1 go out before the values of tile it, in the order in which the stages come free.
+            auto tile_row = [&](int it) {
                 const int key0 = (kt_lo + it) * FT_BN;
                 const int lp = key0 / page_size;
                 int page = lp < max_pages ? bt_row[lp] : -1;
                 if (page < 0 || page >= n_pool_pages) { atomicExch(error_flag, FT_ERR_PAGE); page = 0; }
-                const int row = (page * n_kv + kvh) * page_size + (key0 - lp * page_size);
-                ft_mbar_expect_tx(&ctl->kv_full[s], 2 * FT_KV_BYTES);
-                ft_tma_load_2d(k_tiles + s * FT_KV_BYTES, &map_k, 0, row, &ctl->kv_full[s]);
-                ft_tma_load_2d(k_tiles + s * FT_KV_BYTES + FT_KV_BYTES / 2, &map_k, 64, row, &ctl->kv_full[s]);
-                ft_tma_load_2d(v_tiles + s * FT_KV_BYTES, &map_v, 0, row, &ctl->kv_full[s]);
-                ft_tma_load_2d(v_tiles + s * FT_KV_BYTES + FT_KV_BYTES / 2, &map_v, 64, row, &ctl->kv_full[s]);
-                armed = it + 1;
+                return (page * n_kv + kvh) * page_size + (key0 - lp * page_size);
+            };
+            int armed_k = 0, armed_v = 0;
+            auto load = [&](int it, bool keys) -> bool {
+                const int s = it % FT_STAGES;
+                unsigned long long* empty = keys ? &ctl->k_empty[s] : &ctl->v_empty[s];
+                unsigned long long* full = keys ? &ctl->k_full[s] : &ctl->v_full[s];
+                if (!ft_mbar_wait(empty, ((it / FT_STAGES) & 1) ^ 1, abort)) return false;
+                const int row = tile_row(it);
+                unsigned char* dst = (keys ? k_tiles : v_tiles) + s * FT_KV_BYTES;
+                ft_mbar_expect_tx(full, FT_KV_BYTES);
+                ft_tma_load_2d(dst, keys ? &map_k : &map_v, 0, row, full);
+                ft_tma_load_2d(dst + FT_KV_BYTES / 2, keys ? &map_k : &map_v, 64, row, full);
+                (keys ? armed_k : armed_v) = it + 1;
+                return true;
+            };
+            bool ok = load(0, true);
+            for (int it = 0; it < n_tiles && ok; ++it) {
+                if (it + 1 < n_tiles) ok = load(it + 1, true);
+                if (ok) ok = load(it, false);
             }
-            if (*abort) {
+            if (!ok && !*abort) { *abort = 1; atomicExch(error_flag, FT_ERR_PRODUCER); }
+            if (*abort) {                                // no copy may be in flight when the CTA leaves
                 int never = 0;
                 ft_mbar_wait(&ctl->q_full, 0, &never);
-                for (int i = max(0, armed - FT_STAGES); i < armed; ++i)
-                    ft_mbar_wait(&ctl->kv_full[i % FT_STAGES], (i / FT_STAGES) & 1, &never);
+                for (int i = max(0, armed_k - FT_STAGES); i < armed_k; ++i)
+                    ft_mbar_wait(&ctl->k_full[i % FT_STAGES], (i / FT_STAGES) & 1, &never);
+                for (int i = max(0, armed_v - FT_STAGES); i < armed_v; ++i)
+                    ft_mbar_wait(&ctl->v_full[i % FT_STAGES], (i / FT_STAGES) & 1, &never);
             }
         }
     } else if (warp == 1) {
@@ -222,31 +245,36 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __
             if (!ok && !*abort) { *abort = 1; atomicExch(error_flag, FT_ERR_MMA); }
             auto issue_s = [&](int it) -> bool {
                 const int s = it % FT_STAGES;
-                if (!ft_mbar_wait(&ctl->kv_full[s], (it / FT_STAGES) & 1, abort)) return false;
+                if (!ft_mbar_wait(&ctl->k_full[s], (it / FT_STAGES) & 1, abort)) return false;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t k_addr = ft_smem(k_tiles + s * FT_KV_BYTES);
 #pragma unroll
                 for (int k = 0; k < FT_D / 16; ++k) {
                     const uint32_t qa = q_addr + (k >> 2) * (FT_Q_BYTES / 2) + (k & 3) * 32;
                     const uint32_t ka = k_addr + (k >> 2) * (FT_KV_BYTES / 2) + (k & 3) * 32;
-                    ft_mma_ss(tmem + FT_COL_S, ft_desc_kmajor(qa), ft_desc_kmajor(ka), idesc_s, k != 0);
+                    ft_mma_ss(tmem + FT_COL_S + (it & 1) * FT_BN, ft_desc_kmajor(qa), ft_desc_kmajor(ka), idesc_s, k != 0);
                 }
-                ft_commit(&ctl->s_full);
+                ft_commit(&ctl->s_full[it & 1]);
+                ft_commit(&ctl->k_empty[s]);
                 return true;
             };
             if (ok) ok = issue_s(0);
             for (int it = 0; it < n_tiles && ok; ++it) {
                 const int s = it % FT_STAGES;
-                if (!ft_mbar_wait(&ctl->p_ready, it & 1, abort)) { ok = false; break; }
+                // The scores of the next tile, into the other buffer, while the softmax warps work on this
+                // one.  The products run in the order they are issued, so this one starts after P V of the
+                // tile before, which read its probabilities from that buffer.
+                if (it + 1 < n_tiles && !(ok = issue_s(it + 1))) break;
+                if (!ft_mbar_wait(&ctl->p_ready[it & 1], (it >> 1) & 1, abort) ||
+                    !ft_mbar_wait(&ctl->v_full[s], (it / FT_STAGES) & 1, abort)) { ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t v_addr = ft_smem(v_tiles + s * FT_KV_BYTES);
 #pragma unroll
                 for (int k = 0; k < FT_BN / 16; ++k)     // 16 keys = two groups of 8 rows = 2,048 bytes further
-                    ft_mma_ts(tmem + FT_COL_O, tmem + FT_COL_P + k * 8, ft_desc_mnmajor(v_addr + k * 2048, FT_KV_BYTES / 2),
-                              idesc_o, k != 0);
-                ft_commit(&ctl->o_full);
-                ft_commit(&ctl->kv_empty[s]);            // both products of the tile have read the stage
-                if (it + 1 < n_tiles) ok = issue_s(it + 1);   // runs while the softmax warps fold P V in
+                    ft_mma_ts(tmem + FT_COL_O, tmem + FT_COL_S + (it & 1) * FT_BN + k * 8,
+                              ft_desc_mnmajor(v_addr + k * 2048, FT_KV_BYTES / 2), idesc_o, (it | k) != 0);
+                ft_commit(&ctl->o_done);
+                ft_commit(&ctl->v_empty[s]);
             }
             if (!ok && !*abort) { *abort = 1; atomicExch(error_flag, FT_ERR_MMA); }
         }
@@ -255,75 +283,103 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __
         const int r = q * 32 + lane;                     // this thread's query row = its lane of tensor memory
         const int pos = pos0 + r;
         const uint32_t lane_base = tmem + ((uint32_t)(q * 32) << 16);
-        float o[FT_D];
-#pragma unroll
-        for (int i = 0; i < FT_D; ++i) o[i] = 0.f;
-        float m = -INFINITY, l = 0.f;
+        float ref = -INFINITY, l = 0.f;                  // exponentials are taken against `ref`; l is the sum of them
         bool ok = true;
+        // tensor memory is read and written by whole warps: a wait that gives up does so for the whole warp
+        auto wait_warp = [&](void* bar, uint32_t parity) {
+            const bool w = ft_mbar_wait(bar, parity, abort);
+            return __all_sync(0xffffffffu, w);
+        };
         for (int it = 0; it < n_tiles; ++it) {
-            if (!ft_mbar_wait(&ctl->s_full, it & 1, abort)) { ok = false; break; }
+            const int b = it & 1;
+            if (!wait_warp(&ctl->s_full[b], (it >> 1) & 1)) { ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int key0 = (kt_lo + it) * FT_BN;
-            float s[FT_BN];
+            float s[FT_BN];                              // raw scores: the scale is folded into the exponent below
             {
-                float a[32], b[32];
-                ft_ld32(lane_base + FT_COL_S, a);
-                ft_ld32(lane_base + FT_COL_S + 32, b);
+                float a[32], c[32];
+                ft_ld32(lane_base + FT_COL_S + b * FT_BN, a);
+                ft_ld32(lane_base + FT_COL_S + b * FT_BN + 32, c);
 #pragma unroll
-                for (int j = 0; j < 32; ++j) { s[j] = a[j]; s[32 + j] = b[j]; }
+                for (int j = 0; j < 32; ++j) { s[j] = a[j]; s[32 + j] = c[j]; }
             }
-            float mx = -INFINITY;
+            // tiles that every row of the CTA sees whole need no mask
+            if (key0 + FT_BN - 1 > pos0 || (window > 0 && key0 <= pos0 + FT_BM - 1 - window)) {
 #pragma unroll
-            for (int j = 0; j < FT_BN; ++j) {
-                const int key = key0 + j;
-                const bool seen = key <= pos && (window <= 0 || key > pos - window);
-                s[j] = seen ? s[j] * scale_log2 : -INFINITY;
-                mx = fmaxf(mx, s[j]);
+                for (int j = 0; j < FT_BN; ++j) {
+                    const int key = key0 + j;
+                    const bool seen = key <= pos && (window <= 0 || key > pos - window);
+                    s[j] = seen ? s[j] : -INFINITY;
+                }
             }
-            const float m_new = fmaxf(m, mx);
-            const float use = m_new == -INFINITY ? 0.f : m_new;      // a row that has seen no key yet stays all zero
-            const float corr = exp2f(m - use);
-            m = m_new;
-            float sum = 0.f;
+            float mx4[4] = {s[0], s[1], s[2], s[3]};     // four chains instead of one of 63 dependent steps
+#pragma unroll
+            for (int j = 4; j < FT_BN; ++j) mx4[j & 3] = fmaxf(mx4[j & 3], s[j]);
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;   // the scale is positive
+            if (it == 0) {
+                ref = mx;                                // nothing accumulated yet: nothing to rescale
+            } else {
+                // O must not change under the rescale: P V of the tile before has to be done (it has been
+                // for long, as a rule).  Waited for every tile, so that the barrier's phases are seen in order.
+                if (!wait_warp(&ctl->o_done, (it - 1) & 1)) { ok = false; break; }
+                const bool grow = mx > ref + FT_LAZY;    // also a row that sees its first key (ref = -inf)
+                if (__any_sync(0xffffffffu, grow)) {     // tensor memory is read and written by whole warps
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const float corr = grow ? exp2f(ref - mx) : 1.f;
+#pragma unroll
+                    for (int c4 = 0; c4 < FT_D / 32; ++c4) {
+                        float o[32];
+                        uint32_t u[32];
+                        ft_ld32(lane_base + FT_COL_O + c4 * 32, o);
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) u[j] = __float_as_uint(o[j] * corr);
+                        ft_st32(lane_base + FT_COL_O + c4 * 32, u);
+                    }
+                    l *= corr;
+                    if (grow) ref = mx;
+                }
+            }
+            const float neg_use = ref == -INFINITY ? 0.f : -ref;     // a row that has seen no key yet stays all zero
+            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
             uint32_t pk[32];
 #pragma unroll
             for (int j = 0; j < FT_BN; j += 2) {
-                const float p0 = exp2f(s[j] - use), p1 = exp2f(s[j + 1] - use);
-                sum += p0 + p1;
+                // one multiply-add and one ex2 per score; results below 2^-126 are flushed to zero
+                const float p0 = ft_ex2(fmaf(s[j], scale_log2, neg_use)), p1 = ft_ex2(fmaf(s[j + 1], scale_log2, neg_use));
+                sum4[(j >> 1) & 3] += p0 + p1;
                 __nv_bfloat162 v = __floats2bfloat162_rn(p0, p1);
                 pk[j >> 1] = *reinterpret_cast<uint32_t*>(&v);
             }
-            l = l * corr + sum;
-            ft_st32(lane_base + FT_COL_P, pk);
+            const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+            l += sum;
+            ft_st32(lane_base + FT_COL_S + b * FT_BN, pk);
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
-            if (lane == 0) ft_mbar_arrive(&ctl->p_ready);
-#pragma unroll
-            for (int i = 0; i < FT_D; ++i) o[i] *= corr;
-            if (!ft_mbar_wait(&ctl->o_full, it & 1, abort)) { ok = false; break; }
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll
-            for (int c = 0; c < FT_D / 32; ++c) {
-                float pv[32];
-                ft_ld32(lane_base + FT_COL_O + c * 32, pv);
-#pragma unroll
-                for (int j = 0; j < 32; ++j) o[c * 32 + j] += pv[j];
-            }
+            if (lane == 0) ft_mbar_arrive(&ctl->p_ready[b]);
         }
+        if (ok && !wait_warp(&ctl->o_done, (n_tiles - 1) & 1)) ok = false;
         if (!ok && !*abort) { *abort = 1; atomicExch(error_flag, FT_ERR_SOFTMAX); }
-        if (ok && r < n_rows) {
+        if (ok) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const float inv = l > 0.f ? 1.f / l : 0.f;
             bf16* dst = out + ((size_t)(row0 + r) * n_q + h) * FT_D;
 #pragma unroll
-            for (int i = 0; i < FT_D; i += 8) {
-                uint4 v;
-                __nv_bfloat162 p0 = __floats2bfloat162_rn(o[i] * inv, o[i + 1] * inv);
-                __nv_bfloat162 p1 = __floats2bfloat162_rn(o[i + 2] * inv, o[i + 3] * inv);
-                __nv_bfloat162 p2 = __floats2bfloat162_rn(o[i + 4] * inv, o[i + 5] * inv);
-                __nv_bfloat162 p3 = __floats2bfloat162_rn(o[i + 6] * inv, o[i + 7] * inv);
-                v.x = *reinterpret_cast<uint32_t*>(&p0); v.y = *reinterpret_cast<uint32_t*>(&p1);
-                v.z = *reinterpret_cast<uint32_t*>(&p2); v.w = *reinterpret_cast<uint32_t*>(&p3);
-                *reinterpret_cast<uint4*>(dst + i) = v;
+            for (int c4 = 0; c4 < FT_D / 32; ++c4) {
+                float o[32];
+                ft_ld32(lane_base + FT_COL_O + c4 * 32, o);      // by whole warps, rows beyond the tile too
+                if (r < n_rows) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8) {
+                        uint4 v;
+                        __nv_bfloat162 p0 = __floats2bfloat162_rn(o[i] * inv, o[i + 1] * inv);
+                        __nv_bfloat162 p1 = __floats2bfloat162_rn(o[i + 2] * inv, o[i + 3] * inv);
+                        __nv_bfloat162 p2 = __floats2bfloat162_rn(o[i + 4] * inv, o[i + 5] * inv);
+                        __nv_bfloat162 p3 = __floats2bfloat162_rn(o[i + 6] * inv, o[i + 7] * inv);
+                        v.x = *reinterpret_cast<uint32_t*>(&p0); v.y = *reinterpret_cast<uint32_t*>(&p1);
+                        v.z = *reinterpret_cast<uint32_t*>(&p2); v.w = *reinterpret_cast<uint32_t*>(&p3);
+                        *reinterpret_cast<uint4*>(dst + c4 * 32 + i) = v;
+                    }
+                }
             }
         }
     }

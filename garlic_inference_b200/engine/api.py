@@ -131,3 +131,8 @@ class AutoModel:
     def from_pretrained(model_dir, device=0, **kwargs) -> LanguageModel:
         """The model of the folder on GPU `device`, its class chosen by config.json."""
         return LanguageModel.from_pretrained(model_dir, device=device, **kwargs)
+
+    @staticmethod
+    def from_random(config, seed: int = 0, device=0, **kwargs) -> LanguageModel:
+        """A model of the configuration's sizes with random weights made on GPU `device`."""
+        return LanguageModel.from_random(config, seed=seed, device=device, **kwargs)

@@ -154,9 +154,11 @@ class Engine:
         def runs(rows: int) -> np.ndarray:
             if single:
                 return np.zeros((0, 4), dtype=np.int32)
-            return np.asarray([(s, st + r0, min(rows, n - r0), p + r0)
-                               for s, st, n, p in zip(slots, starts, lens, past) for r0 in range(0, n, rows)],
-                              dtype=np.int32)
+            tiles = [(s, st + r0, min(rows, n - r0), p + r0)
+                     for s, st, n, p in zip(slots, starts, lens, past) for r0 in range(0, n, rows)]
+            # the runs with the most keys to walk go first, so that the last CTAs to start are short ones
+            tiles.sort(key=lambda t: -(t[3] + t[2]))
+            return np.asarray(tiles, dtype=np.int32)
 
         tiles, tiles128 = runs(64), runs(128)
         # the runs go first: the kernels read them 16 bytes at a time

@@ -4,7 +4,7 @@
     python -m garlic_inference_b200.ops.microbench time [linear|attn|prefill|small]   GPU time inside CUDA graphs, cold L2
 
 OP: gemv | skinny | cublas (M = rows of x, SHAPE = qkv | o | gate_up | down | lm_head at Qwen3-8B sizes),
-attn_decode (M = sequences, 2,048 cached tokens each), attn_prefill (M = prompt length).
+attn_decode (M = sequences, 2,048 cached tokens each), attn_prefill and attn_prefill_tcgen05 (M = prompt length).
 `time` rotates over several copies of the operands (more than the 126 MB of L2) and reports the
 algorithmic bytes over the time.
 """
@@ -91,6 +91,16 @@ def run(op: str, m: int, shape: str = "gate_up") -> None:
         tiles = torch.tensor([(0, r, min(64, m - r), r) for r in range(0, m, 64)], dtype=torch.int32, device=DEV)
         for _ in range(4):
             kernels.attention_prefill_bf16(q, k_pool, v_pool, table, tiles, HEAD_DIM ** -0.5, 0)
+    elif op == "attn_prefill_tcgen05":
+        n_pages = -(-m // PAGE)
+        k_pool = torch.randn(n_pages, N_KV, PAGE, HEAD_DIM, device=DEV, dtype=torch.bfloat16)
+        v_pool = torch.randn_like(k_pool)
+        table = torch.arange(n_pages, dtype=torch.int32, device=DEV).view(1, -1)
+        q = torch.randn(m, N_Q, HEAD_DIM, device=DEV, dtype=torch.bfloat16)
+        tiles = torch.tensor([(0, r, min(128, m - r), r) for r in reversed(range(0, m, 128))], dtype=torch.int32, device=DEV)
+        for _ in range(4):
+            kernels.attention_prefill_tcgen05(q, k_pool, v_pool, table, tiles, HEAD_DIM ** -0.5, 0)
+        print("error flag", int(kernels.tcgen05_error_flag(DEV).item()))
     else:
         raise SystemExit(f"unknown op {op}")
     torch.cuda.synchronize()
@@ -166,8 +176,9 @@ def time_prefill_linear(m: int = 2048) -> None:
     v_pool = torch.randn_like(k_pool)
     table = torch.arange(n_pages, dtype=torch.int32, device=DEV).view(1, -1)
     q = torch.randn(m, N_Q, HEAD_DIM, device=DEV, dtype=torch.bfloat16)
-    t64 = torch.tensor([(0, r, min(64, m - r), r) for r in range(0, m, 64)], dtype=torch.int32, device=DEV)
-    t128 = torch.tensor([(0, r, min(128, m - r), r) for r in range(0, m, 128)], dtype=torch.int32, device=DEV)
+    # the runs with the most keys first, as the engine orders them
+    t64 = torch.tensor([(0, r, min(64, m - r), r) for r in reversed(range(0, m, 64))], dtype=torch.int32, device=DEV)
+    t128 = torch.tensor([(0, r, min(128, m - r), r) for r in reversed(range(0, m, 128))], dtype=torch.int32, device=DEV)
     flops = 4.0 * N_Q * HEAD_DIM * m * (m + 1) / 2
     res = {"tcgen05": graph_time([lambda: kernels.attention_prefill_tcgen05(q, k_pool, v_pool, table, t128, HEAD_DIM ** -0.5, 0)] * 3),
            "mma.sync": graph_time([lambda: kernels.attention_prefill_bf16(q, k_pool, v_pool, table, t64, HEAD_DIM ** -0.5, 0)] * 3)}

@@ -98,6 +98,30 @@ def test_command_line(model_dirs):
     assert r2.returncode == 0 and r2.stdout.splitlines()[0].split() == _cut(lines[0].split(), lines[0].split()[1])
 
 
+def test_command_line_prompt_file_and_random_weights(model_dirs, tmp_path):
+    """--prompt-file reads one prompt a line; --random-weights needs a config.json alone and gives the same
+    ids from run to run for one --weights-seed."""
+    prompts = tmp_path / "prompts.txt"
+    prompts.write_text("1 2 3\n\n40,41\n")
+    cmd = [sys.executable, str(tiny.REPO / "bin" / "runner"), str(model_dirs("A")), "--max-new-tokens", "4",
+           "--dtype", "float32", "--prompt-file", str(prompts)]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-3000:]
+    cfg, w = plain.read_model_dir(model_dirs("A"))
+    lines = r.stdout.strip().splitlines()
+    assert [int(t) for t in lines[0].split()] == plain.greedy(cfg, w, [1, 2, 3], 4)
+    assert [int(t) for t in lines[1].split()] == plain.greedy(cfg, w, [40, 41], 4)
+    only_config = tmp_path / "cfg"
+    only_config.mkdir()
+    (only_config / "config.json").write_text((model_dirs("B") / "config.json").read_text())
+    cmd = [sys.executable, str(tiny.REPO / "bin" / "runner"), str(only_config), "--random-weights", "--weights-seed", "5",
+           "--max-new-tokens", "6", "--prompt-ids", "9,8,7"]
+    runs = [subprocess.run(cmd, capture_output=True, text=True, timeout=600) for _ in range(2)]
+    assert all(x.returncode == 0 for x in runs), runs[0].stderr[-3000:]
+    first = runs[0].stdout.splitlines()[0].split()
+    assert len(first) == 6 and first == runs[1].stdout.splitlines()[0].split()
+
+
 def test_smoke_entry():
     sys.path.insert(0, str(tiny.REPO))
     import __graft_entry__ as entry
