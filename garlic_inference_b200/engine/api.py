@@ -55,6 +55,7 @@ class LanguageModel:
         self.sampler = Sampler(model.rt.device)
         self.default_stop_ids = tuple(default_stop_ids)
         self.last_stats = None
+        self.run_ahead = True          # generate() launches each decode step before it has read the last one's tokens
 
     # ---- construction ----------------------------------------------------------------
     @classmethod
@@ -110,6 +111,15 @@ class LanguageModel:
                                    token_indices)
         return toks.tolist()                        # device -> host: the step's only synchronisation
 
+    def _pick_on_device(self, logits, request_ids, token_indices, params: GenParams) -> "_Picked":
+        toks = self.sampler.sample(logits, SamplingParams(params.temperature, params.seed), request_ids,
+                                   token_indices)
+        if not hasattr(self, "_pinned"):            # two pinned buffers, used in turn: a copy per step in flight
+            n = self.engine.cache.max_slots
+            self._pinned, self._pinned_turn = [torch.empty(n, dtype=torch.int32).pin_memory() for _ in range(2)], 0
+        self._pinned_turn ^= 1
+        return _Picked(toks, self._pinned[self._pinned_turn])
+
     def generate(self, prompts: Sequence[Sequence[int]], max_new_tokens: int = 128, temperature: float = 0.0,
                  seed: int = 0, stop_token_ids: Optional[Sequence[int]] = None,
                  max_batch: Optional[int] = None) -> list[list[int]]:
@@ -117,13 +127,47 @@ class LanguageModel:
         params = GenParams(max_new_tokens=max_new_tokens, temperature=temperature, seed=seed,
                            stop_token_ids=self.default_stop_ids if stop_token_ids is None else tuple(stop_token_ids))
         cache = self.engine.cache
+        ahead = self.engine.rt.device.type == "cuda" and self.run_ahead
         loop = GenerationLoop(self.engine, self._pick, capacity_tokens=cache.max_tokens,
                               max_positions=self.model.max_positions,
-                              max_batch=min(max_batch or cache.max_slots, cache.max_slots))
+                              max_batch=min(max_batch or cache.max_slots, cache.max_slots),
+                              device_picker=self._pick_on_device if ahead else None)
         out = loop.run(prompts, params)
         self.last_stats = loop.stats
         self.engine.check()
         return out
+
+
+class _Picked:
+    """The tokens chosen in one step, on the device, with their copy to the host under way."""
+
+    def __init__(self, tokens: torch.Tensor, pinned: Optional[torch.Tensor], host_rows=None, parent=None):
+        self.tokens, self._pinned, self._rows, self._parent = tokens, pinned, host_rows, parent
+        self._event = None
+
+    def start_copy(self) -> None:
+        n = self.tokens.numel()
+        self._pinned[:n].copy_(self.tokens, non_blocking=True)
+        self._event = torch.cuda.Event()
+        self._event.record()
+
+    def to_host(self) -> list:
+        if self._parent is not None:
+            all_rows = self._parent.to_host()
+            return [all_rows[r] for r in self._rows]
+        if not hasattr(self, "_list"):
+            self._event.synchronize()
+            self._list = self._pinned[:self.tokens.numel()].tolist()
+        return self._list
+
+    def select(self, rows) -> torch.Tensor:
+        """The device tokens of the listed rows."""
+        idx = torch.tensor(list(rows), dtype=torch.int64, device=self.tokens.device)
+        return self.tokens.index_select(0, idx).contiguous()
+
+    def narrowed(self, rows) -> "_Picked":
+        """These rows only (the others belonged to requests that have ended since)."""
+        return _Picked(self.select(rows), None, host_rows=list(rows), parent=self)
 
 
 class AutoModel:

@@ -38,8 +38,8 @@ class Sampler:
         n = logits.shape[0]
         if params.temperature <= 0:
             return kernels.sample(logits, None, None, None, 0)
-        host = torch.tensor([list(request_ids), list(token_indices)], dtype=torch.int64)
+        pin = self.device.type == "cuda"               # pinned, so that the copies do not wait for the GPU
+        streams = torch.tensor(list(request_ids), dtype=torch.int64, pin_memory=pin).to(self.device, non_blocking=True)
+        counters = torch.tensor(list(token_indices), dtype=torch.int32, pin_memory=pin).to(self.device, non_blocking=True)
         temps = torch.full((n,), float(params.temperature), dtype=torch.float32, device=self.device)
-        streams = host[0].to(self.device)
-        counters = host[1].to(torch.int32).to(self.device)
         return kernels.sample(logits, temps, streams, counters, params.seed)

@@ -129,3 +129,90 @@ def test_slots_are_given_back_when_a_step_fails():
     with pytest.raises(RuntimeError, match="boom"):
         loop(st, counting_picker([])).run([[1], [2]], GenParams(max_new_tokens=5))
     assert not st.live and len(st.free) == 4
+
+
+# ---- the loop that runs one step ahead of the host --------------------------------------------
+class AheadStepper(ScriptedStepper):
+    """A stepper that also takes a step's tokens 'from the device' (here: a list nobody has read yet)."""
+
+    def __init__(self, n_slots=4):
+        super().__init__(n_slots)
+        self.ahead_calls = []
+
+    def step_decode_device(self, slots, tokens):
+        for s in slots:
+            assert s in self.live, "a step ahead for a slot that has been given back"
+            self.live[s] += 1
+        toks = list(tokens)
+        assert len(toks) == len(slots)
+        self.ahead_calls.append([(s, t) for s, t in zip(slots, toks)])
+        return [(s, [t]) for s, t in zip(slots, toks)]
+
+
+class FakePicked:
+    def __init__(self, tokens, log):
+        self.tokens, self.log, self.copied = list(tokens), log, False
+
+    def start_copy(self):
+        self.copied = True
+
+    def to_host(self):
+        assert self.copied, "tokens read before their copy was started"
+        self.log.append(("read", list(self.tokens)))
+        return list(self.tokens)
+
+    def select(self, rows):
+        return [self.tokens[r] for r in rows]
+
+    def narrowed(self, rows):
+        p = FakePicked([self.tokens[r] for r in rows], self.log)
+        p.copied = True
+        return p
+
+
+def ahead_picker(log, keys):
+    def pick(logits, request_ids, token_indices, params):
+        keys.append((list(request_ids), list(token_indices)))
+        return FakePicked([toks[-1] + 1 for _, toks in logits], log)
+    return pick
+
+
+@pytest.mark.parametrize("prompts,params", [
+    ([[10, 11, 12], [50], [70, 71]], GenParams(max_new_tokens=3)),
+    ([[1], [20], [97]], GenParams(max_new_tokens=6, stop_token_ids=(22, 98))),
+    ([[1], [20], [97]], GenParams(max_new_tokens=1)),
+    ([[5], [30]], GenParams(max_new_tokens=9, stop_token_ids=(8, 33, 34))),
+])
+def test_running_one_step_ahead_returns_what_the_plain_loop_returns(prompts, params):
+    plain_st, plain_keys = ScriptedStepper(), []
+    want = loop(plain_st, counting_picker(plain_keys)).run(prompts, params)
+    st, log, keys = AheadStepper(), [], []
+    lp = GenerationLoop(st, None, 4096, 1000, 4, device_picker=ahead_picker(log, keys))
+    got = lp.run(prompts, params)
+    assert got == want
+    assert not st.live and sorted(st.freed) == sorted(plain_st.freed)
+    assert lp.stats.new_tokens == sum(len(o) for o in want)
+    # every token that was kept was drawn with the same (request, token index) key as in the plain loop
+    kept = {(r, i) for ids, idx in plain_keys for r, i in zip(ids, idx)}
+    drawn = {(r, i) for ids, idx in keys for r, i in zip(ids, idx)}
+    assert kept <= drawn
+
+
+def test_one_step_ahead_launches_before_it_reads_and_never_steps_past_a_known_end():
+    st, log, keys = AheadStepper(), [], []
+    lp = GenerationLoop(st, None, 4096, 1000, 4, device_picker=ahead_picker(log, keys))
+    out = lp.run([[1], [20]], GenParams(max_new_tokens=3, stop_token_ids=(22,)))
+    assert out == [[2, 3, 4], [21, 22]]
+    # step for token 2 of both requests is launched before token 1 is read; request 1 meets its stop token at
+    # token 2, which shows only after the step for token 3 has taken it along: that row is dropped
+    assert st.ahead_calls == [[(0, 2), (1, 21)], [(0, 3), (1, 22)]]
+    assert len(st.calls) == 1                     # the prompts' step; everything after it came from the device
+    assert st.freed == [1, 0]
+
+
+def test_one_step_ahead_respects_the_position_limit():
+    st, log, keys = AheadStepper(), [], []
+    lp = GenerationLoop(st, None, 4096, 5, 4, device_picker=ahead_picker(log, keys))
+    out = lp.run([[1, 2, 3]], GenParams(max_new_tokens=10))
+    assert out == [[4, 5]]                        # 3 + 2 = 5 positions
+    assert st.live == {} and max(len(c) for c in st.ahead_calls) == 1 and len(st.ahead_calls) == 1
