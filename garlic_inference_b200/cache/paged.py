@@ -76,9 +76,11 @@ class _KVGroup:
         rows = sorted(self.host.dirty)
         self.host.dirty.clear()
         idx = torch.as_tensor(rows, dtype=torch.long)
-        src = torch.from_numpy(self.host.table[rows]).pin_memory() if self.table.is_cuda else \
-            torch.from_numpy(self.host.table[rows])
-        self.table.index_copy_(0, idx.to(self.table.device), src.to(self.table.device, non_blocking=True))
+        src = torch.from_numpy(self.host.table[rows])
+        if self.table.is_cuda:                   # pinned, so that neither copy waits for the steps in flight
+            idx, src = idx.pin_memory(), src.pin_memory()
+        self.table.index_copy_(0, idx.to(self.table.device, non_blocking=True),
+                               src.to(self.table.device, non_blocking=True))
 
 
 class PagedCache:

@@ -156,6 +156,28 @@ def time_small(hidden: int = 4096, inter: int = 12288) -> None:
                 status)] * 32),
         }
         print(f"M={m:3d}  " + "  ".join(f"{k}: {v * 1e3:5.2f} us" for k, v in times.items()), flush=True)
+    # the same kernels over a prompt of 2,048 tokens (one sequence, positions 0..2047)
+    m, ctx = 2048, 2048
+    res = torch.randn(m, hidden, device=DEV)
+    delta = torch.randn(m, hidden, device=DEV, dtype=torch.bfloat16)
+    w = torch.ones(hidden, device=DEV, dtype=torch.bfloat16)
+    gate_up = torch.randn(m, 2 * inter, device=DEV, dtype=torch.bfloat16)
+    qkv = torch.randn(m, (N_Q + 2 * N_KV) * HEAD_DIM, device=DEV, dtype=torch.bfloat16)
+    wn = torch.ones(HEAD_DIM, device=DEV, dtype=torch.bfloat16)
+    pools, table, _, _, _ = _decode_case(1, ctx, 1)
+    pos = torch.arange(m, dtype=torch.int32, device=DEV)
+    slot = torch.zeros(m, dtype=torch.int32, device=DEV)
+    cos = torch.randn(ctx, HEAD_DIM // 2, device=DEV)
+    sin = torch.randn(ctx, HEAD_DIM // 2, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    times = {
+        "add_rmsnorm": graph_time([lambda: kernels.add_rmsnorm(delta, res, w, 1e-6, torch.bfloat16)] * 8),
+        "swiglu": graph_time([lambda: kernels.swiglu(gate_up)] * 8),
+        "qk_norm_rope_append": graph_time([lambda: kernels.qk_norm_rope_append(
+            qkv, N_Q, N_KV, HEAD_DIM, wn, wn, 1e-6, cos, sin, HEAD_DIM, pos, slot, pools[0][0], pools[0][1], table,
+            status)] * 8),
+    }
+    print(f"M={m}  " + "  ".join(f"{k}: {v * 1e3:5.2f} us" for k, v in times.items()), flush=True)
 
 
 def time_prefill_linear(m: int = 2048) -> None:
