@@ -358,6 +358,42 @@ def test_qk_norm_rope_append(dtype, n_q, n_kv, d, rot, qk_norm, wdt):
     assert torch.equal(q2, q_out) and float(k2.float().abs().sum()) == 0 and float(v2.float().abs().sum()) == 0
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n_q,n_kv,d", [(5, 1, 64), (8, 2, 128), (3, 3, 192), (1, 1, 256)])
+def test_qk_norm_rope_append_of_a_prompt_equals_token_by_token(dtype, n_q, n_kv, d):
+    """From 256 tokens on a warp takes four heads of a token at a time (groups that hold query, key and
+    value heads at once when the head counts are no multiples of four): the same bits as the same tokens
+    in small steps, which the test above compares with the plain implementation."""
+    from garlic_inference_b200.parts.rotary import RotaryPositions
+    page, n, max_pos = 16, 300, 320
+    g = torch.Generator(device=DEV).manual_seed(n_q * 100 + d)
+    qkv = torch.randn(n, (n_q + 2 * n_kv) * d, generator=g, device=DEV).to(dtype)
+    qw = (1 + 0.2 * torch.randn(d, generator=g, device=DEV)).to(torch.bfloat16)
+    kw = (1 + 0.2 * torch.randn(d, generator=g, device=DEV)).to(torch.bfloat16)
+    cos, sin = (t.to(DEV) for t in RotaryPositions.build_tables(d, 1e4, max_pos))
+    n_pages = max_pos // page
+    bt = torch.randperm(n_pages, generator=torch.Generator().manual_seed(1)).to(torch.int32).view(1, -1).to(DEV)
+    pos = torch.arange(n, dtype=torch.int32, device=DEV)
+    slot = torch.zeros(n, dtype=torch.int32, device=DEV)
+    slot[17] = slot[299] = -1                                   # padding rows: q written, nothing cached
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+
+    def run(cuts):
+        k_pool = torch.zeros(n_pages, n_kv, page, d, dtype=dtype, device=DEV)
+        v_pool = torch.zeros_like(k_pool)
+        outs = [K().qk_norm_rope_append(qkv[a:b].contiguous(), n_q, n_kv, d, qw, kw, 1e-6, cos, sin, d,
+                                        pos[a:b].contiguous(), slot[a:b].contiguous(), k_pool, v_pool, bt, status)
+                for a, b in cuts]
+        return torch.cat(outs), k_pool, v_pool
+
+    whole = run([(0, n)])
+    pieces = run([(a, min(a + 100, n)) for a in range(0, n, 100)])
+    assert int(status.item()) == 0
+    for a, b in zip(whole, pieces):
+        assert torch.equal(a, b)
+    assert float(whole[1][bt[0, 1].item(), :, 1].float().abs().sum()) == 0      # position 17: padding
+
+
 def test_out_of_range_indices_set_the_status_and_touch_nothing():
     n_q, n_kv, d, page = 2, 1, 16, 8
     qkv = torch.ones(2, (n_q + 2) * d, device=DEV)
