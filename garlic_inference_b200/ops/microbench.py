@@ -3,7 +3,7 @@
     python -m garlic_inference_b200.ops.microbench run  OP M [SHAPE]     a few plain launches (what ncu captures)
     python -m garlic_inference_b200.ops.microbench time [linear|attn|prefill|small]   GPU time inside CUDA graphs, cold L2
 
-OP: gemv | skinny | cublas (M = rows of x, SHAPE = qkv | o | gate_up | down | lm_head at Qwen3-8B sizes),
+OP: gemv | skinny | cublas | tcgen05 (M = rows of x, SHAPE = qkv | o | gate_up | down | lm_head at Qwen3-8B sizes),
 attn_decode (M = sequences, 2,048 cached tokens each), attn_prefill and attn_prefill_tcgen05 (M = prompt length).
 `time` rotates over several copies of the operands (more than the 126 MB of L2) and reports the
 algorithmic bytes over the time.
@@ -58,6 +58,8 @@ def _linear(op: str, x, w):
         return kernels.gemm_skinny_bf16(x, w, torch.bfloat16)
     if op == "cublas":
         return torch.mm(x, w.t())
+    if op == "tcgen05":
+        return kernels.gemm_tcgen05_bf16(x, w, torch.bfloat16)
     raise SystemExit(f"unknown op {op}")
 
 
@@ -73,7 +75,7 @@ def _decode_case(batch: int, ctx: int, copies: int):
 
 
 def run(op: str, m: int, shape: str = "gate_up") -> None:
-    if op in ("gemv", "skinny", "cublas"):
+    if op in ("gemv", "skinny", "cublas", "tcgen05"):
         ws = _weights(shape, 3)
         x = torch.randn(m, SHAPES[shape][1], device=DEV, dtype=torch.bfloat16)
         for i in range(6):
