@@ -4,6 +4,6 @@ the compiled library), `linear` (the choice of matrix product) and `library`
 operation does."""
 from . import kernels
 from .library import ExtensionError, KernelError, counters, lib, require_gpu
-from .linear import linear
+from .linear import linear, swiglu_product
 
-__all__ = ["kernels", "linear", "lib", "require_gpu", "ExtensionError", "KernelError", "counters"]
+__all__ = ["kernels", "linear", "swiglu_product", "lib", "require_gpu", "ExtensionError", "KernelError", "counters"]

@@ -252,6 +252,21 @@ def gemm_tcgen05_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) 
     return out
 
 
+def gemm_tcgen05_swiglu_bf16(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
+    """silu(x . Wg^T) * (x . Wu^T) for w_gate_up = [Wg; Wu] ([2 I, K], the gate first): the gate/up product of
+    a SwiGLU feed-forward with the activation in the epilogue of the tcgen05 product (pairs of CTAs).
+    Returns [M, I] bfloat16, the bits of `swiglu(gemm_tcgen05_bf16(x, w_gate_up))`."""
+    l = require_gpu()
+    _dense(x, "x", torch.bfloat16), _dense(w_gate_up, "w_gate_up", torch.bfloat16)
+    (m, k), (n2, k2) = x.shape, w_gate_up.shape
+    if k != k2:
+        raise KernelError(f"inner sizes differ: x {tuple(x.shape)}, w {tuple(w_gate_up.shape)}")
+    out = torch.empty((m, n2 // 2), dtype=torch.bfloat16, device=x.device)
+    check(l.gi_gemm_tcgen05_swiglu_bf16(_ptr(x), _ptr(w_gate_up), _ptr(out), m, n2, k,
+                                        _ptr(tcgen05_error_flag(x.device)), _stream()), l)
+    return out
+
+
 def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor], streams: Optional[torch.Tensor],
            counters: Optional[torch.Tensor], seed: int, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """One token per row of float32 logits [n, vocab]: greedy where temperature <= 0 (or None),

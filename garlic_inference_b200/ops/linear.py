@@ -28,6 +28,11 @@ from .library import KernelError
 # GARLIC_B200_GEMM=tcgen05 (or this variable) to run this package's kernel instead.
 LARGE_GEMM = os.environ.get("GARLIC_B200_GEMM", "library")
 
+# From how many rows of x on the gate/up product of a SwiGLU feed-forward runs as this package's tcgen05
+# kernel with the activation in its epilogue (bfloat16).  Measured at 2,048 rows and Qwen3-8B sizes: 295 us
+# against 276 us for the library product plus 33 us for the SwiGLU kernel.  0 switches it off.
+FUSED_SWIGLU_MIN_ROWS = int(os.environ.get("GARLIC_B200_FUSED_SWIGLU_ROWS", "512"))
+
 GEMV_MAX_ROWS = 1          # one row: the plain bandwidth kernel
 SKINNY_MAX_ROWS = 8        # up to here: the tensor-core kernel that streams W once (it takes 16; the library is faster from 9 on)
 
@@ -56,3 +61,14 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
     if out_dtype == torch.float32:
         return torch.mm(x, w.t(), out_dtype=torch.float32)
     return torch.mm(x, w.t())
+
+
+def swiglu_product(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
+    """silu(x . Wg^T) * (x . Wu^T) for the packed weight [Wg; Wu]: prompts in bfloat16 run it as one tcgen05
+    kernel (product and activation), everything else as the product of `linear` and the SwiGLU kernel."""
+    m, k = x.shape
+    if (FUSED_SWIGLU_MIN_ROWS > 0 and m >= FUSED_SWIGLU_MIN_ROWS and x.dtype == torch.bfloat16
+            and w_gate_up.dtype == torch.bfloat16 and k % 8 == 0 and w_gate_up.shape[0] % 2 == 0
+            and x.data_ptr() % 16 == 0 and w_gate_up.data_ptr() % 16 == 0):
+        return kernels.gemm_tcgen05_swiglu_bf16(x, w_gate_up)
+    return kernels.swiglu(linear(x, w_gate_up))

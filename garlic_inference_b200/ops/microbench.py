@@ -194,6 +194,13 @@ def time_prefill_linear(m: int = 2048) -> None:
                "cublas": graph_time([(lambda w=w, x=x: torch.mm(x, w.t())) for w, x in zip(ws, xs)])}
         print(f"{shape:8s} M={m}  " + "  ".join(f"{op}: {ms * 1e3:7.1f} us {flops / ms / 1e9:6.0f} TFLOP/s"
                                                 for op, ms in res.items()), flush=True)
+    # the gate/up product with the SwiGLU in its epilogue against the library product and the SwiGLU kernel
+    ws = _weights("gate_up", 3)
+    xs = [torch.randn(m, SHAPES["gate_up"][1], device=DEV, dtype=torch.bfloat16) for _ in range(3)]
+    res = {"tcgen05 fused": graph_time([(lambda w=w, x=x: kernels.gemm_tcgen05_swiglu_bf16(x, w)) for w, x in zip(ws, xs)]),
+           "cublas + swiglu": graph_time([(lambda w=w, x=x: kernels.swiglu(torch.mm(x, w.t()))) for w, x in zip(ws, xs)])}
+    print(f"gate_up+swiglu M={m}  " + "  ".join(f"{op}: {ms * 1e3:7.1f} us" for op, ms in res.items()), flush=True)
+    del ws, xs
     # causal attention of the same prompt: 4 * n_q * d * m^2 / 2 flops
     n_pages = -(-m // PAGE)
     k_pool = torch.randn(n_pages, N_KV, PAGE, HEAD_DIM, device=DEV, dtype=torch.bfloat16)

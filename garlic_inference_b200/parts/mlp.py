@@ -7,7 +7,7 @@ from __future__ import annotations
 
 import torch
 
-from ..ops import kernels, linear
+from ..ops import linear, swiglu_product
 from ..weights.loader import TensorWant
 from .base import FeedForward, register_part
 
@@ -30,8 +30,7 @@ class SwiGLUMLP(FeedForward):
         self.w_down = load("down_proj")
 
     def step(self, x, ctx):
-        gate_up = linear(x, self.w_gate_up)
-        return linear(kernels.swiglu(gate_up), self.w_down)
+        return linear(swiglu_product(x, self.w_gate_up), self.w_down)
 
 
 register_part(SwiGLUMLP.kind, SwiGLUMLP)

@@ -148,6 +148,27 @@ def test_gemm_skinny_bf16(m, n, k, split, wide):
     assert torch.equal(out32, K().gemm_skinny_bf16(x, w, torch.float32, n_split=split, wide=wide)), "same bits from run to run"
 
 
+@pytest.mark.parametrize("m,inter,k", [(300, 128, 64), (2048, 320, 256), (513, 1000, 4096), (129, 136, 72), (1, 264, 1288),
+                                       (1024, 12288, 512)])
+def test_gemm_tcgen05_swiglu_bf16(m, inter, k):
+    """The gate/up product with the SwiGLU in its epilogue: the bits of the plain tcgen05 product followed by
+    the SwiGLU kernel, and close to a float32 computation of both."""
+    g = torch.Generator(device=DEV).manual_seed(m + inter + k)
+    x = torch.randn(m, k, generator=g, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(2 * inter, k, generator=g, device=DEV) * (2.0 / math.sqrt(k))).to(torch.bfloat16)
+    flag = K().tcgen05_error_flag(x.device)
+    flag.zero_()
+    fused = K().gemm_tcgen05_swiglu_bf16(x, w)
+    two_steps = K().swiglu(K().gemm_tcgen05_bf16(x, w, torch.bfloat16))
+    torch.cuda.synchronize()
+    assert int(flag.item()) == 0, "a bounded wait of the kernel ran out"
+    assert fused.shape == (m, inter) and torch.equal(fused, two_steps)
+    gu = x.float() @ w.float().T
+    gate, up = gu[:, :inter].to(torch.bfloat16).float(), gu[:, inter:].to(torch.bfloat16).float()
+    ref = gate / (1 + torch.exp(-gate)) * up
+    torch.testing.assert_close(fused.float(), ref, rtol=3e-2, atol=3e-2)
+
+
 @pytest.mark.parametrize("m,n,k", [(128, 256, 64), (2048, 512, 256), (300, 1000, 4096), (1, 264, 72), (129, 257 * 8, 1288),
                                    (2048, 6144, 4096)])
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
