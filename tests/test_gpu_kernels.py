@@ -148,7 +148,7 @@ def test_gemm_skinny_bf16(m, n, k, split, wide):
     assert torch.equal(out32, K().gemm_skinny_bf16(x, w, torch.float32, n_split=split, wide=wide)), "same bits from run to run"
 
 
-@pytest.mark.parametrize("m,inter,k", [(300, 128, 64), (2048, 320, 256), (513, 1000, 4096), (129, 136, 72), (1, 264, 1288),
+@pytest.mark.parametrize("m,inter,k", [(300, 128, 64), (300, 100, 64), (257, 7, 128), (2048, 320, 256), (513, 1000, 4096), (129, 136, 72), (1, 264, 1288),
                                        (1024, 12288, 512)])
 def test_gemm_tcgen05_swiglu_bf16(m, inter, k):
     """The gate/up product with the SwiGLU in its epilogue: the bits of the plain tcgen05 product followed by
