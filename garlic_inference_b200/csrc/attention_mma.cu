@@ -295,7 +295,7 @@ decode_splitkv_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_poo
                       const int* __restrict__ tok_slot, float* __restrict__ part_o, float* __restrict__ part_ml,
                       int n_q, int n_kv, int page_size, int max_pages, int n_pool_pages, int window,
                       float scale_log2, int n_splits) {
-    gi_pdl_start();
+    gi_pdl_launch_dependents();
     constexpr int LD = D + 8, CH = D / 8;
     constexpr int STAGE = 2 * 16 * LD;                           // elements of one warp's stage: 16 keys, 16 values
     extern __shared__ __align__(16) unsigned char at_smem[];
@@ -313,6 +313,7 @@ decode_splitkv_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_poo
     const int per = (nt_all + n_splits - 1) / n_splits;
     const int t0 = split * per, t1 = min(nt_all, t0 + per);
     float* my_ml = part_ml + (((size_t)b * n_q + kvh * grp) * n_splits + split) * 2;
+    gi_pdl_wait();                               // positions and slots above are set before the step's first kernel
     if (t0 >= t1) {                                              // nothing for this slice: an empty partial
         if (threadIdx.x < grp) {
             my_ml[(size_t)threadIdx.x * n_splits * 2] = -INFINITY;

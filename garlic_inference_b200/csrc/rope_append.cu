@@ -109,7 +109,7 @@ __global__ void qk_norm_rope_append_vec_kernel(
     const int* __restrict__ tok_pos, const int* __restrict__ tok_slot, const int* __restrict__ block_table,
     int n_tokens, int n_q, int n_kv, int page_size, int max_pages, int n_pool_pages,
     int max_positions, int append, int* __restrict__ status) {
-    gi_pdl_start();
+    gi_pdl_launch_dependents();
     constexpr int d = EPL * 32, half = d / 2;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int heads_here = append ? n_q + 2 * n_kv : n_q;
@@ -118,32 +118,24 @@ __global__ void qk_norm_rope_append_vec_kernel(
     if (item >= (long long)n_tokens * groups) return;
     const int t = (int)(item / groups);
     const int h0 = (int)(item - (long long)t * groups) * ROPE_GROUP;
-    const T* src = qkv + (size_t)t * (n_q + 2 * n_kv) * d + lane * EPL;
-    T raw[ROPE_GROUP][EPL];
-#pragma unroll
-    for (int g = 0; g < ROPE_GROUP; ++g)
-        if (h0 + g < heads_here) {
-#pragma unroll
-            for (int e = 0; e < EPL; e += 2) {       // EPL is even: two elements (4 or 8 bytes) at a time
-                raw[g][e] = src[(size_t)(h0 + g) * d + e];
-                raw[g][e + 1] = src[(size_t)(h0 + g) * d + e + 1];
-            }
-        }
+    // Positions, slots, the block table and the rotation table are set before the step's first kernel and
+    // change in none of them: they are read before the wait for the kernel that makes qkv.
     const int pos = tok_pos[t];
     // where this token's keys and values go, if any head of the group is one
     T* k_dst = nullptr;
     T* v_dst = nullptr;
     bool cache_ok = false;
+    int bad = 0;
     if (h0 + ROPE_GROUP > n_q && append) {
         const int slot = tok_slot[t];
         if (slot >= 0) {
             const int lp = pos / page_size;
             if (pos < 0 || lp >= max_pages) {
-                if (lane == 0) atomicExch(status, 1);
+                bad = 1;
             } else {
                 const int page = block_table[(size_t)slot * max_pages + lp];
                 if (page < 0 || page >= n_pool_pages) {
-                    if (lane == 0) atomicExch(status, 2);
+                    bad = 2;
                 } else {
                     const size_t row = (size_t)page * n_kv * page_size + (pos - lp * page_size);
                     k_dst = k_pool + row * d + lane * EPL;
@@ -162,6 +154,19 @@ __global__ void qk_norm_rope_append_vec_kernel(
             sn[e] = sin_t[(size_t)pos * half + (lane & 15) * EPL + e];
         }
     }
+    gi_pdl_wait();
+    if (bad && lane == 0) atomicExch(status, bad);
+    const T* src = qkv + (size_t)t * (n_q + 2 * n_kv) * d + lane * EPL;
+    T raw[ROPE_GROUP][EPL];
+#pragma unroll
+    for (int g = 0; g < ROPE_GROUP; ++g)
+        if (h0 + g < heads_here) {
+#pragma unroll
+            for (int e = 0; e < EPL; e += 2) {       // EPL is even: two elements (4 or 8 bytes) at a time
+                raw[g][e] = src[(size_t)(h0 + g) * d + e];
+                raw[g][e + 1] = src[(size_t)(h0 + g) * d + e + 1];
+            }
+        }
 #pragma unroll
     for (int g = 0; g < ROPE_GROUP; ++g) {
         const int h = h0 + g;
