@@ -252,6 +252,36 @@ def gemm_tcgen05_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) 
     return out
 
 
+_streamk_space: dict = {}
+
+
+def _streamk_workspace(device):
+    """Per device: the float32 slots through which the CTAs of the stream-K product hand over partial tiles,
+    and their flags (zero between calls: every call clears what it set)."""
+    key = torch.device(device).index or 0
+    if key not in _streamk_space:
+        l = require_gpu()
+        _streamk_space[key] = (torch.empty(l.gi_gemm_streamk_workspace_floats(), dtype=torch.float32, device=device),
+                               torch.zeros(l.gi_gemm_streamk_flags(), dtype=torch.int32, device=device))
+    return _streamk_space[key]
+
+
+def gemm_streamk_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """x [M<=16, K] . w[N,K]^T on tcgen05 with W cut evenly over the SMs (TMA-fed, operands swapped: the rows of
+    W fill the 128-row side of the instruction).  Calls on one device share a work space, so they must not
+    overlap (they do not on one stream)."""
+    l = require_gpu()
+    _dense(x, "x", torch.bfloat16), _dense(w, "w", torch.bfloat16)
+    (m, k), (n, k2) = x.shape, w.shape
+    if k != k2:
+        raise KernelError(f"inner sizes differ: x {tuple(x.shape)}, w {tuple(w.shape)}")
+    out = torch.empty((m, n), dtype=out_dtype, device=x.device)
+    partials, flags = _streamk_workspace(x.device)
+    check(l.gi_gemm_streamk_bf16(_ptr(x), _ptr(w), _ptr(out), code(out_dtype), m, n, k, _ptr(partials), _ptr(flags),
+                                 _ptr(tcgen05_error_flag(x.device)), _stream()), l)
+    return out
+
+
 def gemm_tcgen05_swiglu_bf16(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
     """silu(x . Wg^T) * (x . Wu^T) for w_gate_up = [Wg; Wu] ([2 I, K], the gate first): the gate/up product of
     a SwiGLU feed-forward with the activation in the epilogue of the tcgen05 product (pairs of CTAs).

@@ -40,6 +40,9 @@ _SIGNATURES = {
     "gi_gemv_bf16": ([P, P, P, I, I, I, I, P], I),
     "gi_gemm_skinny_bf16": ([P, P, P, I, I, I, I, I, I, P], I),
     "gi_gemm_tcgen05_swiglu_bf16": ([P, P, P, I, I, I, P, P], I),
+    "gi_gemm_streamk_bf16": ([P, P, P, I, I, I, I, P, P, P, P], I),
+    "gi_gemm_streamk_workspace_floats": ([], L),
+    "gi_gemm_streamk_flags": ([], I),
     "gi_gemm_tcgen05_bf16": ([P, P, P, I, I, I, I, P, P], I),
     "gi_sample": ([P, L, I, I, P, P, P, c_ulonglong, P, P, P, P], I),
     "gi_sample_chunks": ([I], I),

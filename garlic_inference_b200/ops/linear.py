@@ -33,6 +33,12 @@ LARGE_GEMM = os.environ.get("GARLIC_B200_GEMM", "library")
 # against 276 us for the library product plus 33 us for the SwiGLU kernel.  0 switches it off.
 FUSED_SWIGLU_MIN_ROWS = int(os.environ.get("GARLIC_B200_FUSED_SWIGLU_ROWS", "512"))
 
+# Which kernel takes bfloat16 products of 1 to 8 rows whose weight has at least this many bytes: the stream-K
+# tcgen05 kernel (W cut evenly over the SMs, 6.6 TB/s once it runs but about 10 us to start and to merge the
+# cut tiles).  Measured at 8 rows: 189 against 216 us on the 1.24 GB head, 39.4 against 38.9 us on 201 MB,
+# 27.8 against 22.8 us on 101 MB; so smaller weights stay with the gemv / skinny kernels.  0 switches it off.
+STREAMK_MIN_BYTES = int(os.environ.get("GARLIC_B200_STREAMK_MIN_BYTES", str(256 << 20)))
+
 GEMV_MAX_ROWS = 1          # one row: the plain bandwidth kernel
 SKINNY_MAX_ROWS = 8        # up to here: the tensor-core kernel that streams W once (it takes 16; the library is faster from 9 on)
 
@@ -52,6 +58,8 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
     if m == 0:
         return torch.empty((0, w.shape[0]), dtype=out_dtype, device=x.device)
     if m <= SKINNY_MAX_ROWS and k % 8 == 0 and w.data_ptr() % 16 == 0 and x.data_ptr() % 16 == 0:
+        if 0 < STREAMK_MIN_BYTES <= w.numel() * 2:
+            return kernels.gemm_streamk_bf16(x, w, out_dtype)
         if m <= GEMV_MAX_ROWS:
             return kernels.gemv_bf16(x, w, out_dtype)
         return kernels.gemm_skinny_bf16(x, w, out_dtype)

@@ -3,7 +3,7 @@
     python -m garlic_inference_b200.ops.microbench run  OP M [SHAPE]     a few plain launches (what ncu captures)
     python -m garlic_inference_b200.ops.microbench time [linear|attn|prefill|small]   GPU time inside CUDA graphs, cold L2
 
-OP: gemv | skinny | cublas | tcgen05 (M = rows of x, SHAPE = qkv | o | gate_up | down | lm_head at Qwen3-8B sizes),
+OP: gemv | skinny | streamk | cublas | tcgen05 (M = rows of x, SHAPE = qkv | o | gate_up | down | lm_head at Qwen3-8B sizes),
 attn_decode (M = sequences, 2,048 cached tokens each), attn_prefill and attn_prefill_tcgen05 (M = prompt length).
 `time` rotates over several copies of the operands (more than the 126 MB of L2) and reports the
 algorithmic bytes over the time.
@@ -60,6 +60,8 @@ def _linear(op: str, x, w):
         return torch.mm(x, w.t())
     if op == "tcgen05":
         return kernels.gemm_tcgen05_bf16(x, w, torch.bfloat16)
+    if op == "streamk":
+        return kernels.gemm_streamk_bf16(x, w, torch.bfloat16)
     raise SystemExit(f"unknown op {op}")
 
 
@@ -75,7 +77,7 @@ def _decode_case(batch: int, ctx: int, copies: int):
 
 
 def run(op: str, m: int, shape: str = "gate_up") -> None:
-    if op in ("gemv", "skinny", "cublas", "tcgen05"):
+    if op in ("gemv", "skinny", "cublas", "tcgen05", "streamk"):
         ws = _weights(shape, 3)
         x = torch.randn(m, SHAPES[shape][1], device=DEV, dtype=torch.bfloat16)
         for i in range(6):
@@ -115,7 +117,7 @@ def time_linear() -> None:
         ws = _weights(shape, copies)
         for m in (1, 2, 4, 8, 16, 64):
             x = torch.randn(m, k, device=DEV, dtype=torch.bfloat16)
-            ops = (["gemv"] if m <= 8 else []) + (["skinny"] if m <= 16 else []) + ["cublas"]
+            ops = (["gemv"] if m <= 8 else []) + (["skinny", "streamk"] if m <= 16 else []) + ["cublas"]
             res = {op: graph_time([(lambda w=w, op=op: _linear(op, x, w)) for w in ws]) for op in ops}
             print(f"{shape:8s} M={m:3d}  " + "  ".join(f"{op}: {ms * 1e3:7.1f} us {n * k * 2 / ms / 1e6:5.0f} GB/s"
                                                         for op, ms in res.items()), flush=True)

@@ -148,6 +148,31 @@ def test_gemm_skinny_bf16(m, n, k, split, wide):
     assert torch.equal(out32, K().gemm_skinny_bf16(x, w, torch.float32, n_split=split, wide=wide)), "same bits from run to run"
 
 
+@pytest.mark.parametrize("m,n,k", [(1, 128, 64), (8, 100, 1000), (5, 264, 4096), (16, 4096, 4096), (8, 24576, 512), (3, 777, 72),
+                                   (8, 4096, 12288), (2, 151936, 256), (13, 6144, 4096)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_gemm_streamk_bf16(m, n, k, out_dtype):
+    """The decode product that cuts W evenly over the SMs: tiles whose parts lie in several CTAs are summed in
+    one order (same bits from run to run), and the flags are clear again after every call."""
+    g = torch.Generator(device=DEV).manual_seed(m * 1000 + n + k)
+    x = torch.randn(m, k, generator=g, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(n, k, generator=g, device=DEV) * 0.1).to(torch.bfloat16)
+    flag = K().tcgen05_error_flag(x.device)
+    flag.zero_()
+    out = K().gemm_streamk_bf16(x, w, out_dtype)
+    again = K().gemm_streamk_bf16(x, w, out_dtype)
+    torch.cuda.synchronize()
+    assert int(flag.item()) == 0, "a bounded wait of the kernel ran out"
+    ref = x.float() @ w.float().T
+    if out_dtype == torch.float32:
+        torch.testing.assert_close(out, ref, rtol=1e-4, atol=2e-4 * math.sqrt(k))
+    else:
+        torch.testing.assert_close(out.float(), ref.to(torch.bfloat16).float(), **ulp_tol(torch.bfloat16))
+    assert torch.equal(out, again), "same bits from run to run"
+    from garlic_inference_b200.ops.kernels import _streamk_workspace
+    assert int(_streamk_workspace(x.device)[1].abs().sum().item()) == 0, "a flag was left set"
+
+
 @pytest.mark.parametrize("m,inter,k", [(300, 128, 64), (300, 100, 64), (257, 7, 128), (2048, 320, 256), (513, 1000, 4096), (129, 136, 72), (1, 264, 1288),
                                        (1024, 12288, 512)])
 def test_gemm_tcgen05_swiglu_bf16(m, inter, k):
