@@ -198,3 +198,17 @@ def test_tcgen05_products_in_the_model(model_dirs, plain_cache, monkeypatch):
         got = tiny.run_trace_in_process(model, steps)
         tiny.assert_covers(got, reqs)
         tiny.compare(got, want, tiny.TOL["bfloat16"], "D bfloat16 with tcgen05 products")
+
+
+def test_streamk_products_in_the_model(model_dirs, plain_cache, monkeypatch):
+    """Decode steps (recorded and replayed) with the stream-K tcgen05 kernel taking every product of 1 to 8
+    rows, which by default it does only for weights of 256 MB and more."""
+    import sys
+    from garlic_inference_b200 import AutoModel
+    monkeypatch.setattr(sys.modules["garlic_inference_b200.ops.linear"], "STREAMK_MIN_BYTES", 1)
+    reqs, want = plain_cache("D")
+    model = AutoModel.from_pretrained(model_dirs("D"), device=0, dtype="bfloat16", max_tokens=2048, page_size=64)
+    for steps in (tiny.trace_tail_by_one(reqs, tail=32), tiny.trace_batched(reqs, BATCHES, prompt_frac=0.5)):
+        got = tiny.run_trace_in_process(model, steps)
+        tiny.assert_covers(got, reqs)
+        tiny.compare(got, want, tiny.TOL["bfloat16"], "D bfloat16 with stream-K products")
