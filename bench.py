@@ -5,8 +5,8 @@
 
 One JSON line on stdout.  `value` is decoded tokens a second at batch 8 with 2,048 cached tokens
 per sequence (a step = one decode step of the whole batch), timed on the device with the sampler's
-tokens fed back on the device; `e2e` is the same through `LanguageModel.generate` with host token
-ids in and out every step.  `prefill` is one 2,048-token prompt, `points` decoding at batch 1 and
+tokens fed back on the device; `e2e` is the same through `LanguageModel.generate` (prompts and
+generated ids on the host, every step's ids read back), over the last K of W + K + 1 steps.  `prefill` is one 2,048-token prompt, `points` decoding at batch 1 and
 64, `roofline` the bytes a decode step has to read (every weight once, the cache of the live
 requests) over its time against the measured copy bandwidth.
 
@@ -220,18 +220,20 @@ def main() -> int:
             points[f"decode_b{b}"] = time_decode(b)[0]
 
     # ---- the same through the entry point: host ids in, host ids out, every step ------------------
+    # W + K + 1 tokens per request; the clock runs over the last K steps (the W before them are the warm-up,
+    # as in the device-timed loop above), read from the loop's own record of when each step's tokens arrived
     prompts = [random_prompt(CACHED) for _ in range(args.batch)]
     model.generate(prompts[:1], max_new_tokens=4)                           # warm the path
     up0 = eng.bytes_uploaded
     clocks.start()
-    out = model.generate(prompts, max_new_tokens=K + 1)
+    out = model.generate(prompts, max_new_tokens=W + K + 1)
     clocks.stop()
     st = model.last_stats
-    e2e_steps = st.steps - 1
-    e2e = {"value": args.batch * e2e_steps / st.decode_seconds, "unit": "tokens/s",
+    assert all(len(o) == W + K + 1 for o in out) and len(st.step_times) == W + K + 1
+    e2e_seconds = st.step_times[-1] - st.step_times[-1 - K]
+    e2e = {"value": args.batch * K / e2e_seconds, "unit": "tokens/s",
            "h2d_bytes_per_step": (eng.bytes_uploaded - up0) / st.steps,
            "d2h_bytes_per_step": 4 * args.batch}
-    assert all(len(o) == K + 1 for o in out)
 
     line = {
         "metric": f"decode tok/s at batch {args.batch} (Qwen3-8B layer sizes, {CACHED} cached tokens per sequence)",

@@ -57,6 +57,7 @@ class GenStats:
     prefill_seconds: float = 0.0
     decode_seconds: float = 0.0
     batch_sizes: list = field(default_factory=list)     # live requests at each step
+    step_times: list = field(default_factory=list)      # host clock (perf_counter) when each step's tokens had arrived
 
 
 def tokens_held(prompt_len: int, max_new_tokens: int, max_positions: int) -> int:
@@ -132,6 +133,7 @@ class GenerationLoop:
             while True:
                 st.steps += 1
                 st.batch_sizes.append(len(live))
+                st.step_times.append(time.perf_counter())
                 still = []
                 for i, tok in zip(live, tokens):
                     out[i].append(int(tok))
@@ -188,6 +190,7 @@ class GenerationLoop:
                     t0, first = time.perf_counter(), False
                 st.steps += 1
                 st.batch_sizes.append(len(live))
+                st.step_times.append(time.perf_counter())
                 still = []
                 for i, tok in zip(live, tokens):
                     out[i].append(int(tok))
