@@ -542,3 +542,19 @@ extern "C" int gi_attention_decode_bf16(const void* q, const void* k_pool, const
 #undef CALL
     return gi_check_launch("gi_attention_decode_bf16");
 }
+
+// Merges the slices' partial results of a split-KV decode kernel (this file's or the tcgen05 one):
+// part_o float32 [rows * n_splits * d] unnormalised, part_ml float32 [rows * n_splits * 2] = (maximum in
+// powers of two, sum); out bfloat16 [rows, d] for rows = sequences * query heads.
+extern "C" int gi_attention_decode_combine(const float* part_o, const float* part_ml, void* out, int rows, int d,
+                                           int n_splits, void* stream) {
+    GI_REQUIRE(rows >= 0 && n_splits >= 1, "gi_attention_decode_combine: sizes");
+    GI_REQUIRE(d >= 16 && d <= 128 && d % 16 == 0, "gi_attention_decode_combine: head_dim %d", d);
+    if (rows == 0) return 0;
+#define CALL(DD)                                                                                                 \
+    gi_launch(decode_combine_kernel<DD>, dim3(rows), dim3(DD < 128 ? (DD < 32 ? 32 : DD) : 128), 0, (cudaStream_t)stream, \
+              part_o, part_ml, (bf16*)out, n_splits);
+    AT_DISPATCH_D(d, CALL)
+#undef CALL
+    return gi_check_launch("gi_attention_decode_combine");
+}

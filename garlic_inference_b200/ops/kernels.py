@@ -396,6 +396,37 @@ def decode_splits(n_seqs: int, n_kv: int) -> int:
     return 2 if pairs < 1776 else 1
 
 
+def tcgen05_decode_takes(dtype: torch.dtype, head_dim: int, page_size: int, group: int) -> bool:
+    return dtype == torch.bfloat16 and head_dim == 128 and page_size % 64 == 0 and group <= 16
+
+
+def attention_decode_tcgen05(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: torch.Tensor,
+                             tok_pos: torch.Tensor, tok_slot: torch.Tensor, scale: float, window: int,
+                             n_splits: Optional[int] = None) -> torch.Tensor:
+    """Split-KV attention for decode steps on TMA and tcgen05: the arguments of `attention_decode_bf16`; heads
+    of 128, pages that are a multiple of 64 tokens, at most 16 query heads per key/value head."""
+    l = require_gpu()
+    _dense(q, "q", torch.bfloat16), _dense(k_pool, "k_pool", torch.bfloat16), _dense(v_pool, "v_pool", torch.bfloat16)
+    for t, name in ((tok_pos, "tok_pos"), (tok_slot, "tok_slot"), (block_table, "block_table")):
+        _dense(t, name, torch.int32)
+    n, n_q, d = q.shape
+    n_pages, n_kv, page_size, pool_d = k_pool.shape
+    if pool_d != d or v_pool.shape != k_pool.shape:
+        raise KernelError(f"cache pools {tuple(k_pool.shape)} do not fit head_dim {d}")
+    if tok_pos.numel() < n or tok_slot.numel() < n:
+        raise KernelError("tok_pos / tok_slot are shorter than the token rows")
+    n_splits = n_splits or decode_splits(n, n_kv)
+    out = torch.empty((n, n_q * d), dtype=q.dtype, device=q.device)
+    part_o = torch.empty((n * n_q * n_splits * d,), dtype=torch.float32, device=q.device)
+    part_ml = torch.empty((n * n_q * n_splits * 2,), dtype=torch.float32, device=q.device)
+    check(l.gi_attention_decode_tcgen05(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_table), _ptr(tok_pos),
+                                        _ptr(tok_slot), _ptr(part_o), _ptr(part_ml), n, n_q, n_kv, d, page_size,
+                                        block_table.shape[1], n_pages, int(window or 0), float(scale), n_splits,
+                                        _ptr(tcgen05_error_flag(q.device)), _stream()), l)
+    check(l.gi_attention_decode_combine(_ptr(part_o), _ptr(part_ml), _ptr(out), n * n_q, d, n_splits, _stream()), l)
+    return out
+
+
 def attention_decode_bf16(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: torch.Tensor,
                           tok_pos: torch.Tensor, tok_slot: torch.Tensor, scale: float, window: int,
                           n_splits: Optional[int] = None) -> torch.Tensor:

@@ -4,7 +4,7 @@
     python -m garlic_inference_b200.ops.microbench time [linear|attn|prefill|small]   GPU time inside CUDA graphs, cold L2
 
 OP: gemv | skinny | streamk | cublas | tcgen05 (M = rows of x, SHAPE = qkv | o | gate_up | down | lm_head at Qwen3-8B sizes),
-attn_decode (M = sequences, 2,048 cached tokens each), attn_prefill and attn_prefill_tcgen05 (M = prompt length).
+attn_decode and attn_decode_tcgen05 (M = sequences, 2,048 cached tokens each), attn_prefill and attn_prefill_tcgen05 (M = prompt length).
 `time` rotates over several copies of the operands (more than the 126 MB of L2) and reports the
 algorithmic bytes over the time.
 """
@@ -86,6 +86,11 @@ def run(op: str, m: int, shape: str = "gate_up") -> None:
         pools, table, q, pos, slot = _decode_case(m, 2048, 2)
         for i in range(6):
             kernels.attention_decode_bf16(q, pools[i % 2][0], pools[i % 2][1], table, pos, slot, HEAD_DIM ** -0.5, 0)
+    elif op == "attn_decode_tcgen05":
+        pools, table, q, pos, slot = _decode_case(m, 2048, 2)
+        for i in range(6):
+            kernels.attention_decode_tcgen05(q, pools[i % 2][0], pools[i % 2][1], table, pos, slot, HEAD_DIM ** -0.5, 0)
+        print("error flag", int(kernels.tcgen05_error_flag(DEV).item()))
     elif op == "attn_prefill":
         n_pages = -(-m // PAGE)
         k_pool = torch.randn(n_pages, N_KV, PAGE, HEAD_DIM, device=DEV, dtype=torch.bfloat16)
@@ -132,7 +137,10 @@ def time_attention() -> None:
             pools, table, q, pos, slot = _decode_case(batch, ctx, copies)
             ms = graph_time([(lambda p=p: kernels.attention_decode_bf16(q, p[0], p[1], table, pos, slot,
                                                                          HEAD_DIM ** -0.5, 0)) for p in pools])
-            print(f"attn_decode batch={batch:3d} ctx={ctx}  {ms * 1e3:7.1f} us  {nbytes / ms / 1e6:5.0f} GB/s "
+            ms2 = graph_time([(lambda p=p: kernels.attention_decode_tcgen05(q, p[0], p[1], table, pos, slot,
+                                                                            HEAD_DIM ** -0.5, 0)) for p in pools])
+            print(f"attn_decode batch={batch:3d} ctx={ctx}  mma.sync {ms * 1e3:7.1f} us  {nbytes / ms / 1e6:5.0f} GB/s  "
+                  f"tcgen05 {ms2 * 1e3:7.1f} us  {nbytes / ms2 / 1e6:5.0f} GB/s  "
                   f"(slices {kernels.decode_splits(batch, N_KV)})", flush=True)
             del pools
 

@@ -78,14 +78,18 @@ class GQAAttention(Mixer):
     def attend(self, q, kv, ctx):
         """Attention of q [n, n_q, d] over the cache; returns [n, n_q * d].
 
-        Runs of tokens in bfloat16 with heads of 128 and pages that are a multiple of 64 tokens: the
-        tcgen05 flash kernel.  Otherwise bfloat16 with a head size the mma.sync kernels take: the
-        split-KV kernel when every sequence brings one token, the flash kernel for runs of tokens.  Everything
-        else (float32, other head sizes, groups beyond 16 in decode) goes to the exact-order kernel."""
+        bfloat16 with heads of 128 and pages that are a multiple of 64 tokens: the tcgen05 kernels (flash
+        attention for runs of tokens, split-KV when every sequence brings one token and the group is at most
+        16).  Otherwise bfloat16 with a head size the mma.sync kernels take: the split-KV kernel for single
+        tokens, the flash kernel for runs.  Everything else (float32, other head sizes, larger groups in
+        decode) goes to the exact-order kernel."""
         if (not ctx.all_single and ctx.q_tiles128 is not None
                 and kernels.tcgen05_attention_takes(q.dtype, self.d, kv.page_size)):
             return kernels.attention_prefill_tcgen05(q, kv.k_pool, kv.v_pool, kv.block_table, ctx.q_tiles128,
                                                      self.scale, self.window or 0)
+        if ctx.all_single and kernels.tcgen05_decode_takes(q.dtype, self.d, kv.page_size, self.n_q // self.n_kv):
+            return kernels.attention_decode_tcgen05(q, kv.k_pool, kv.v_pool, kv.block_table, ctx.tok_pos, ctx.tok_slot,
+                                                    self.scale, self.window or 0)
         if kernels.mma_attention_takes(q.dtype, self.d):
             if ctx.all_single and self.n_q // self.n_kv <= 16:
                 return kernels.attention_decode_bf16(q, kv.k_pool, kv.v_pool, kv.block_table, ctx.tok_pos,

@@ -554,6 +554,56 @@ def test_attention_decode_bf16(n_q, n_kv, d, page, window, splits):
         torch.testing.assert_close(out[i], ref, rtol=2e-2, atol=2e-2, msg=lambda msg: f"seq {s}: {msg}")
 
 
+@pytest.mark.parametrize("n_q,n_kv,page,window,splits", [(4, 4, 64, 0, 1), (8, 2, 64, 0, 3), (5, 1, 128, 0, 2), (16, 1, 64, 0, 4),
+                                                         (4, 2, 64, 70, 2), (2, 1, 128, 200, 5), (32, 8, 64, 0, 0),
+                                                         (32, 8, 64, 100, 16)])
+def test_attention_decode_tcgen05(n_q, n_kv, page, window, splits):
+    d = 128
+    lens = [1, 37, 300, 64, 65, 130, 513]
+    k_pool, v_pool, bt, kd, vd = make_cache(len(lens), lens, n_kv, d, page, torch.bfloat16, seed=page + n_q + 2)
+    slots = [0, 1, 2, 3, -1, 4, 5, 6]                                   # one padding row in the middle
+    pos = [lens[s] - 1 if s >= 0 else 0 for s in slots]
+    g = torch.Generator(device=DEV).manual_seed(21)
+    q = torch.randn(len(slots), n_q, d, generator=g, device=DEV).to(torch.bfloat16)
+    scale = d ** -0.5
+    flag = K().tcgen05_error_flag(q.device)
+    flag.zero_()
+    out = K().attention_decode_tcgen05(q, k_pool, v_pool, bt, torch.tensor(pos, dtype=torch.int32, device=DEV),
+                                       torch.tensor(slots, dtype=torch.int32, device=DEV), scale, window,
+                                       n_splits=splits or None).float().view(len(slots), n_q, d)
+    torch.cuda.synchronize()
+    assert int(flag.item()) == 0, "a bounded wait of the kernel ran out"
+    for i, s in enumerate(slots):
+        if s < 0:
+            assert float(out[i].abs().sum()) == 0, "a padding row gives zeros"
+            continue
+        ref = ref_attention(q[i].float(), kd[s], vd[s], pos[i], scale, window).float()
+        torch.testing.assert_close(out[i], ref, rtol=2e-2, atol=2e-2, msg=lambda msg: f"seq {s}: {msg}")
+
+
+def test_attention_decode_tcgen05_finds_one_far_key():
+    """One key among 700 carries all the weight, wherever it lies (a page's edge, the first and the last
+    position, another slice): the value of that key comes out; a window that ends just short of it loses it."""
+    n_q, n_kv, d, page, n = 4, 2, 128, 64, 700
+    pos = torch.tensor([n - 1], dtype=torch.int32, device=DEV)
+    slot = torch.zeros(1, dtype=torch.int32, device=DEV)
+    for far in (0, 1, 63, 64, 127, 128, 333, 639, 640, 698, 699):
+        k_pool, v_pool, bt, kd, vd = make_cache(1, [n], n_kv, d, page, torch.bfloat16, seed=far + 5)
+        q = torch.zeros(1, n_q, d, device=DEV)
+        for h in range(n_q):
+            q[0, h] = kd[0][far, h // 2] * 2.0
+        q = q.to(torch.bfloat16)
+        for splits in (1, 3):
+            out = K().attention_decode_tcgen05(q, k_pool, v_pool, bt, pos, slot, 1.0, 0, n_splits=splits).float().view(n_q, d)
+            for h in range(n_q):
+                torch.testing.assert_close(out[h], vd[0][far, h // 2], rtol=2e-2, atol=2e-2,
+                                           msg=lambda msg: f"far key {far}, head {h}, {splits} slices: {msg}")
+        if far < n - 40:
+            gone = K().attention_decode_tcgen05(q, k_pool, v_pool, bt, pos, slot, 1.0, n - 1 - far).float().view(n_q, d)
+            assert float((gone[0] - vd[0][far, 0]).abs().max()) > 0.1, "the window's edge lets it in"
+    assert int(K().tcgen05_error_flag(q.device).item()) == 0
+
+
 def _tiles128_for(runs):
     out = []
     for slot, row0, n, pos0 in runs:
