@@ -141,7 +141,7 @@ def time_attention() -> None:
                                                                             HEAD_DIM ** -0.5, 0)) for p in pools])
             print(f"attn_decode batch={batch:3d} ctx={ctx}  mma.sync {ms * 1e3:7.1f} us  {nbytes / ms / 1e6:5.0f} GB/s  "
                   f"tcgen05 {ms2 * 1e3:7.1f} us  {nbytes / ms2 / 1e6:5.0f} GB/s  "
-                  f"(slices {kernels.decode_splits(batch, N_KV)})", flush=True)
+                  f"(slices {kernels.decode_splits(batch, N_KV)} / {kernels.decode_splits_tcgen05(batch, N_KV)})", flush=True)
             del pools
 
 
