@@ -14,7 +14,8 @@
 //                      reads its row of S, masks the edges (position, window), writes exp2(s - ref) over S as
 //                      bfloat16; ref follows the running maximum lazily as in the prompt kernel.
 // At the end lane r writes its unnormalised row of O with (ref, sum) to the slice's place in the scratch
-// buffers; the combine kernel of the mma.sync path merges the slices.
+// buffers; the combine kernel of the mma.sync path merges the slices.  With one slice there is nothing to
+// merge: the row goes to the output, normalised, and no second kernel runs.
 //
 // Every wait on an mbarrier is bounded; when one runs out a code goes to *error_flag, all roles leave their
 // loops, copies in flight are waited for, tensor memory is freed and the kernel returns.
@@ -141,7 +142,7 @@ __global__ void __launch_bounds__(FD_THREADS, 2)
 decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                       const __grid_constant__ CUtensorMap map_v, const int* __restrict__ block_table,
                       const int* __restrict__ tok_pos, const int* __restrict__ tok_slot, float* __restrict__ part_o,
-                      float* __restrict__ part_ml, int n_q, int n_kv, int page_size, int max_pages, int n_pool_pages,
+                      float* __restrict__ part_ml, bf16* __restrict__ out, int n_q, int n_kv, int page_size, int max_pages, int n_pool_pages,
                       int window, float scale_log2, int n_splits, int* __restrict__ error_flag) {
     gi_pdl_launch_dependents();
     extern __shared__ unsigned char fd_raw[];
@@ -167,7 +168,9 @@ decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
 
     if (n_tiles == 0) {                                                  // nothing for this slice: an empty partial
         gi_pdl_wait();
-        if (threadIdx.x < grp) {
+        if (n_splits == 1) {                                             // no slices: the output itself, zeros
+            for (int i = threadIdx.x; i < grp * FD_D; i += FD_THREADS) out[row_base * FD_D + i] = __float2bfloat16_rn(0.f);
+        } else if (threadIdx.x < grp) {
             float* ml = part_ml + ((row_base + threadIdx.x) * n_splits + split) * 2;
             ml[0] = -INFINITY;
             ml[1] = 0.f;
@@ -353,17 +356,31 @@ decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         if (ok) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             float* dst = part_o + ((row_base + r) * n_splits + split) * FD_D;
+            bf16* whole = out + (row_base + r) * FD_D;                   // without slices the output is written here
+            const float inv = l > 0.f ? 1.f / l : 0.f;
 #pragma unroll
             for (int c4 = 0; c4 < FD_D / 32; ++c4) {
                 float o[32];
                 fd_ld32(lane_base + FD_COL_O + c4 * 32, o);              // by the whole warp
-                if (mine) {
+                if (mine && n_splits > 1) {
 #pragma unroll
                     for (int i = 0; i < 32; i += 4)
                         *reinterpret_cast<float4*>(dst + c4 * 32 + i) = make_float4(o[i], o[i + 1], o[i + 2], o[i + 3]);
+                } else if (mine) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8) {
+                        uint4 v;
+                        __nv_bfloat162 p0 = __floats2bfloat162_rn(o[i] * inv, o[i + 1] * inv);
+                        __nv_bfloat162 p1 = __floats2bfloat162_rn(o[i + 2] * inv, o[i + 3] * inv);
+                        __nv_bfloat162 p2 = __floats2bfloat162_rn(o[i + 4] * inv, o[i + 5] * inv);
+                        __nv_bfloat162 p3 = __floats2bfloat162_rn(o[i + 6] * inv, o[i + 7] * inv);
+                        v.x = *reinterpret_cast<uint32_t*>(&p0); v.y = *reinterpret_cast<uint32_t*>(&p1);
+                        v.z = *reinterpret_cast<uint32_t*>(&p2); v.w = *reinterpret_cast<uint32_t*>(&p3);
+                        *reinterpret_cast<uint4*>(whole + c4 * 32 + i) = v;
+                    }
                 }
             }
-            if (mine) {
+            if (mine && n_splits > 1) {
                 float* ml = part_ml + ((row_base + r) * n_splits + split) * 2;
                 ml[0] = l > 0.f ? ref : -INFINITY;       // a slice in which this row saw no key counts as empty
                 ml[1] = l;
@@ -411,10 +428,11 @@ static int fd_make_map(CUtensorMap* map, const void* base, long long rows, long 
 
 // The slices' partial results: part_o float32 [n_seqs * n_q * n_splits * 128] (unnormalised), part_ml float32
 // [n_seqs * n_q * n_splits * 2] (reference in powers of two, sum); gi_attention_decode_combine merges them.
+// With n_splits == 1 the kernel writes out [n_seqs, n_q * 128] bfloat16 itself and the scratch is not touched.
 // Takes head_dim 128, page sizes that are a multiple of 64 and groups of at most 16 query heads.
 extern "C" int gi_attention_decode_tcgen05(const void* q, const void* k_pool, const void* v_pool, const int* block_table,
                                            const int* tok_pos, const int* tok_slot, float* part_o, float* part_ml,
-                                           int n_seqs, int n_q, int n_kv, int d, int page_size, int max_pages,
+                                           void* out, int n_seqs, int n_q, int n_kv, int d, int page_size, int max_pages,
                                            int n_pool_pages, int window, float scale, int n_splits, int* error_flag,
                                            void* stream) {
     GI_REQUIRE(d == FD_D, "gi_attention_decode_tcgen05: head_dim %d; this kernel takes 128", d);
@@ -425,7 +443,8 @@ extern "C" int gi_attention_decode_tcgen05(const void* q, const void* k_pool, co
                "gi_attention_decode_tcgen05: sizes");
     GI_REQUIRE(error_flag != nullptr, "gi_attention_decode_tcgen05: an error flag on the device is required");
     GI_REQUIRE(((uintptr_t)q % 16 == 0) && ((uintptr_t)k_pool % 16 == 0) && ((uintptr_t)v_pool % 16 == 0) &&
-               ((uintptr_t)part_o % 16 == 0), "gi_attention_decode_tcgen05: operands must start on 16 bytes");
+               ((uintptr_t)part_o % 16 == 0) && ((uintptr_t)out % 16 == 0), "gi_attention_decode_tcgen05: operands must start on 16 bytes");
+    GI_REQUIRE(out != nullptr && (n_splits == 1 || (part_o != nullptr && part_ml != nullptr)), "gi_attention_decode_tcgen05: buffers");
     if (n_seqs == 0) return 0;
     CUtensorMap map_q, map_k, map_v;
     if (int rc = fd_make_map(&map_q, q, (long long)n_seqs * n_q, d, FD_QROWS)) return rc;
@@ -440,7 +459,7 @@ extern "C" int gi_attention_decode_tcgen05(const void* q, const void* k_pool, co
         attr_done = true;
     }
     gi_launch(decode_tcgen05_kernel, dim3(n_splits, n_kv, n_seqs), dim3(FD_THREADS), smem, (cudaStream_t)stream, map_q, map_k,
-              map_v, block_table, tok_pos, tok_slot, part_o, part_ml, n_q, n_kv, page_size, max_pages, n_pool_pages, window,
+              map_v, block_table, tok_pos, tok_slot, part_o, part_ml, (bf16*)out, n_q, n_kv, page_size, max_pages, n_pool_pages, window,
               scale * 1.4426950408889634f, n_splits, error_flag);
     return gi_check_launch("gi_attention_decode_tcgen05");
 }

@@ -425,13 +425,16 @@ def attention_decode_tcgen05(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torc
         raise KernelError("tok_pos / tok_slot are shorter than the token rows")
     n_splits = n_splits or decode_splits_tcgen05(n, n_kv)
     out = torch.empty((n, n_q * d), dtype=q.dtype, device=q.device)
-    part_o = torch.empty((n * n_q * n_splits * d,), dtype=torch.float32, device=q.device)
-    part_ml = torch.empty((n * n_q * n_splits * 2,), dtype=torch.float32, device=q.device)
+    part_o = part_ml = None
+    if n_splits > 1:
+        part_o = torch.empty((n * n_q * n_splits * d,), dtype=torch.float32, device=q.device)
+        part_ml = torch.empty((n * n_q * n_splits * 2,), dtype=torch.float32, device=q.device)
     check(l.gi_attention_decode_tcgen05(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_table), _ptr(tok_pos),
-                                        _ptr(tok_slot), _ptr(part_o), _ptr(part_ml), n, n_q, n_kv, d, page_size,
+                                        _ptr(tok_slot), _ptr(part_o), _ptr(part_ml), _ptr(out), n, n_q, n_kv, d, page_size,
                                         block_table.shape[1], n_pages, int(window or 0), float(scale), n_splits,
                                         _ptr(tcgen05_error_flag(q.device)), _stream()), l)
-    check(l.gi_attention_decode_combine(_ptr(part_o), _ptr(part_ml), _ptr(out), n * n_q, d, n_splits, _stream()), l)
+    if n_splits > 1:                                 # one slice: the kernel wrote the output itself
+        check(l.gi_attention_decode_combine(_ptr(part_o), _ptr(part_ml), _ptr(out), n * n_q, d, n_splits, _stream()), l)
     return out
 
 

@@ -36,7 +36,7 @@ _SIGNATURES = {
     "gi_attention_prefill_tcgen05": ([P, P, P, P, P, I, P, I, I, I, I, I, I, I, I, F, P, P], I),
     "gi_attention_decode_bf16": ([P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, P], I),
     "gi_set_pdl": ([I], None),
-    "gi_attention_decode_tcgen05": ([P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, P, P], I),
+    "gi_attention_decode_tcgen05": ([P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, P, P], I),
     "gi_attention_decode_combine": ([P, P, P, I, I, I, P], I),
     "gi_sgemm_nt": ([P, P, P, I, I, I, L, L, P], I),
     "gi_gemv_bf16": ([P, P, P, I, I, I, I, P], I),
