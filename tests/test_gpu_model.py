@@ -15,8 +15,9 @@ LENGTHS = {
     "B": [5, 11, 2, 300, 97, 64, 129],
     "C": [90, 41, 40, 200, 17, 3, 130],
     "D": [300, 64, 1, 129, 700, 65, 128],
+    "E": [260, 101, 100, 64, 400, 99, 129],
 }
-PAGE = {"A": 16, "B": 16, "C": 16, "D": 64}
+PAGE = {"A": 16, "B": 16, "C": 16, "D": 64, "E": 64}
 BATCHES = [["r0", "r1", "r2"], ["r3", "r4"], ["r5", "r6"]]
 
 
@@ -39,7 +40,7 @@ def plain_cache(model_dirs):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_every_cutting_agrees_with_the_plain_implementation(name, dtype, gpu_models, plain_cache):
     reqs, want = plain_cache(name)
     tol = tiny.TOL[dtype]

@@ -4,7 +4,7 @@ Configurations of the architecture that differ in every size and option:
 layers, width (one no power of two), heads and groups (2, 6 and 1 query heads
 per key/value head), head sizes 16 / 32 / 48, feed-forward width, vocabulary,
 rope theta, the norms' eps, positions, tied or separate head, and the window
-(none; none; 40 keys on the two middle layers of four).
+(none; none; 40 keys on the two middle layers of four; none; 100 keys on the outer layers of three).
 """
 from __future__ import annotations
 
@@ -39,6 +39,13 @@ TINY = {
                        head_dim=128, intermediate_size=320, vocab_size=600, rope_theta=1e6, rms_norm_eps=1e-6,
                        max_position_embeddings=1024, tie_word_embeddings=False),
               seed=3, std=0.04, norm_std=0.1),
+    # heads of 128 with a window of 100 keys on the first and the last of three layers, one key/value head for
+    # four query heads: the tcgen05 kernels with windows, and pages of a window group given back while decoding
+    "E": dict(cfg=dict(hidden_size=192, num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=1,
+                       head_dim=128, intermediate_size=224, vocab_size=400, rope_theta=1e5, rms_norm_eps=2e-6,
+                       max_position_embeddings=1024, tie_word_embeddings=True, sliding_window=100,
+                       layer_types=["sliding_attention", "full_attention", "sliding_attention"]),
+              seed=4, std=0.05, norm_std=0.1),
 }
 
 # tolerances (never widened to pass): float32 logits against the plain float32 implementation,
