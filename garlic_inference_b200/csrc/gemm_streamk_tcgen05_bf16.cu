@@ -6,7 +6,8 @@
 // CTA c of G (one per SM) takes the blocks [c U / G, (c + 1) U / G) of the U blocks in that order, whatever
 // the shape is.  Its range is at most the tail of one tile, some whole tiles, and the head of one tile:
 //   warp 0, one lane:  TMA.  Block after block, 128 x 64 of W (16 KB) and the 16 x 64 of x that go with
-//                      it (2 KB, rows beyond M zero-filled) into a ring of ten shared-memory stages.
+//                      it (2 KB, rows beyond M zero-filled) into a ring of ten shared-memory stages (six when
+//                      every CTA takes one whole tile, see the entry point).
 //   warp 1, one lane:  MMA.  The operands are swapped: the 128 rows of W are the 128-row operand of
 //                      tcgen05.mma, the batch is the 16-wide one; a tile's part accumulates in one of two
 //                      accumulators of 16 columns in tensor memory.
@@ -28,8 +29,8 @@
 #define SKT_ROWS 128                    // rows of W per tile
 #define SKT_BK 64
 #define SKT_BN 16                       // the batch, padded
-#define SKT_STAGES 10                   // 180 KB of ring: 160 KB of W in flight per SM (six stages, so that two CTAs fit an SM
-                                        // and the next product starts under this one, measured slower: 196 vs 189 us on the head)
+#define SKT_MAX_STAGES 10               // 180 KB of ring: 160 KB of W in flight per SM, one CTA per SM (the cut-evenly mode)
+#define SKT_FEW_STAGES 6                // 108 KB: two CTAs per SM (the mode of one whole tile per CTA)
 #define SKT_THREADS 192
 #define SKT_W_BYTES (SKT_ROWS * SKT_BK * 2)
 #define SKT_X_BYTES (SKT_BN * SKT_BK * 2)
@@ -44,8 +45,8 @@
 #define SKT_ERR_PARTIAL 34
 
 struct SktControl {
-    unsigned long long full[SKT_STAGES];
-    unsigned long long empty[SKT_STAGES];
+    unsigned long long full[SKT_MAX_STAGES];
+    unsigned long long empty[SKT_MAX_STAGES];
     unsigned long long acc_full[2];
     unsigned long long acc_empty[2];
     unsigned int tmem_base;
@@ -122,7 +123,7 @@ __device__ __forceinline__ SktSegment skt_segment(long long u, long long u1, int
     return s;
 }
 
-template <int OUT_F32>
+template <int OUT_F32, int SKT_STAGES>
 __global__ void __launch_bounds__(SKT_THREADS, 1)
 gemm_streamk_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                             void* __restrict__ out, float* __restrict__ partials, int* __restrict__ flags,
@@ -356,6 +357,18 @@ static int skt_make_map(CUtensorMap* map, const void* base, int rows, int K, int
     return 0;
 }
 
+#include <stdlib.h>
+#include <string.h>
+// GARLIC_B200_STREAMK_WHOLE_TILES=0 keeps every shape in the cut-evenly mode.
+static bool gi_streamk_whole_tiles_enabled() {
+    static int on = -1;
+    if (on < 0) {
+        const char* v = getenv("GARLIC_B200_STREAMK_WHOLE_TILES");
+        on = (v && strcmp(v, "0") == 0) ? 0 : 1;
+    }
+    return on == 1;
+}
+
 // Floats of work space and ints of flags the entry point below wants (for any shape): one slot and one flag
 // per CTA.  The flags must be zero before the first call; every call leaves them zero.
 extern "C" long long gi_gemm_streamk_workspace_floats(void) { return (long long)SKT_MAX_CTAS * SKT_SLOT_FLOATS; }
@@ -374,24 +387,33 @@ extern "C" int gi_gemm_streamk_bf16(const void* x, const void* W, void* out, int
         int dev = 0;
         if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
     }
-    const long long units = (long long)((N + SKT_ROWS - 1) / SKT_ROWS) * ((K + SKT_BK - 1) / SKT_BK);
-    long long g = units < n_sm ? units : n_sm;           // all CTAs resident at once: they wait for one another
-    if (g > SKT_MAX_CTAS) g = SKT_MAX_CTAS;
+    const long long n_tiles = (N + SKT_ROWS - 1) / SKT_ROWS;
+    const long long units = n_tiles * ((K + SKT_BK - 1) / SKT_BK);
+    // Two ways to share W out.  When there are between one and two tiles of 128 rows per SM, every CTA takes one
+    // whole tile, two CTAs to an SM: nothing is cut, nothing merged, and with enough bytes in flight per CTA the
+    // memory system serves all of them at the same pace however they are spread over the SMs.  Otherwise the
+    // blocks are cut evenly over one CTA per SM and the cut tiles merged (the kernel's main text).
+    const bool whole_tiles = n_tiles >= n_sm && n_tiles <= 2LL * n_sm && gi_streamk_whole_tiles_enabled();
+    long long g = whole_tiles ? n_tiles : (units < n_sm ? units : n_sm);   // cut mode: all CTAs resident at once, they wait for one another
+    if (!whole_tiles && g > SKT_MAX_CTAS) g = SKT_MAX_CTAS;
     CUtensorMap map_w, map_x;
     if (int rc = skt_make_map(&map_w, W, N, K, SKT_ROWS)) return rc;
     if (int rc = skt_make_map(&map_x, x, M, K, SKT_BN)) return rc;
-    const size_t smem = (size_t)SKT_STAGES * (SKT_W_BYTES + SKT_X_BYTES) + sizeof(SktControl) + 1024;
+    const int stages = whole_tiles ? SKT_FEW_STAGES : SKT_MAX_STAGES;
+    const size_t smem = (size_t)stages * (SKT_W_BYTES + SKT_X_BYTES) + sizeof(SktControl) + 1024;
     const int f32 = out_dtype == GI_DTYPE_F32;
-    static bool attr_done[2] = {false, false};
-    if (!attr_done[f32]) {
-        cudaError_t e = f32 ? cudaFuncSetAttribute((const void*)gemm_streamk_tcgen05_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
-                            : cudaFuncSetAttribute((const void*)gemm_streamk_tcgen05_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    static bool attr_done[2][2] = {{false, false}, {false, false}};
+    const void* fn = f32 ? (whole_tiles ? (const void*)gemm_streamk_tcgen05_kernel<1, SKT_FEW_STAGES> : (const void*)gemm_streamk_tcgen05_kernel<1, SKT_MAX_STAGES>)
+                         : (whole_tiles ? (const void*)gemm_streamk_tcgen05_kernel<0, SKT_FEW_STAGES> : (const void*)gemm_streamk_tcgen05_kernel<0, SKT_MAX_STAGES>);
+    if (!attr_done[f32][whole_tiles]) {
+        cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) { gi_set_error("gi_gemm_streamk_bf16: shared memory: %s", cudaGetErrorString(e)); return (int)e; }
-        attr_done[f32] = true;
+        attr_done[f32][whole_tiles] = true;
     }
-    if (f32) gi_launch(gemm_streamk_tcgen05_kernel<1>, dim3((unsigned)g), dim3(SKT_THREADS), smem, (cudaStream_t)stream, map_w, map_x,
-                       out, partials, flags, M, N, K, error_flag);
-    else gi_launch(gemm_streamk_tcgen05_kernel<0>, dim3((unsigned)g), dim3(SKT_THREADS), smem, (cudaStream_t)stream, map_w, map_x,
-                   out, partials, flags, M, N, K, error_flag);
+#define SKT_LAUNCH(F, S) gi_launch(gemm_streamk_tcgen05_kernel<F, S>, dim3((unsigned)g), dim3(SKT_THREADS), smem, (cudaStream_t)stream, \
+                                   map_w, map_x, out, partials, flags, M, N, K, error_flag)
+    if (f32) { if (whole_tiles) SKT_LAUNCH(1, SKT_FEW_STAGES); else SKT_LAUNCH(1, SKT_MAX_STAGES); }
+    else { if (whole_tiles) SKT_LAUNCH(0, SKT_FEW_STAGES); else SKT_LAUNCH(0, SKT_MAX_STAGES); }
+#undef SKT_LAUNCH
     return gi_check_launch("gi_gemm_streamk_bf16");
 }
