@@ -49,7 +49,8 @@
 #define FT_ERR_PAGE 24
 
 struct FtControl {
-    unsigned long long q_full;
+    unsigned long long q_full, q_empty;
+    unsigned long long o_free;
     unsigned long long k_full[FT_STAGES], k_empty[FT_STAGES];
     unsigned long long v_full[FT_STAGES], v_empty[FT_STAGES];
     unsigned long long s_full[2];
@@ -144,10 +145,16 @@ __device__ __forceinline__ void ft_st32(uint32_t taddr, const uint32_t (&u)[32])
 }
 
 // tiles[t] = {slot, first row of q, rows in the tile (<= 128), position of the first row}
+//
+// The grid is persistent: at most two CTAs per SM walk the list of (tile, head) items, CTA c of G taking the
+// items c, 2G - 1 - c, 2G + c, 4G - 1 - c, ... : with the tiles sorted by the keys they walk, longest first
+// (the engine sorts them), every CTA gets a long item with a short one and they finish together.
+struct FtItem { int slot, row0, n_rows, pos0, h, kvh, kt_lo, n_tiles; };
+
 __global__ void __launch_bounds__(FT_THREADS, 2)
 flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                              const __grid_constant__ CUtensorMap map_v, const int* __restrict__ block_table,
-                             const int4* __restrict__ tiles, bf16* __restrict__ out, int n_q, int n_kv,
+                             const int4* __restrict__ tiles, int n_q_tiles, bf16* __restrict__ out, int n_q, int n_kv,
                              int page_size, int max_pages, int n_pool_pages, int window, float scale_log2,
                              int* __restrict__ error_flag) {
     gi_pdl_start();
@@ -158,18 +165,29 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __
     unsigned char* v_tiles = k_tiles + FT_STAGES * FT_KV_BYTES;
     FtControl* ctl = reinterpret_cast<FtControl*>(v_tiles + FT_STAGES * FT_KV_BYTES);
 
-    const int4 ti = tiles[blockIdx.x];
-    const int slot = ti.x, row0 = ti.y, n_rows = ti.z, pos0 = ti.w;
-    const int h = blockIdx.y, kvh = h / (n_q / n_kv);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int hi = pos0 + n_rows - 1;
-    const int lo = window > 0 ? max(0, pos0 - window + 1) : 0;
-    const int kt_lo = lo / FT_BN;
-    const int n_tiles = (slot < 0 || n_rows <= 0) ? 0 : hi / FT_BN - kt_lo + 1;
+    const long long n_items = (long long)n_q_tiles * n_q;
+    const int G = gridDim.x, c = blockIdx.x;
+    // item of round `round` of this CTA: 1 = there is one, 0 = none in this round, -1 = no more rounds
+    auto item_at = [&](int round, FtItem& it) -> int {
+        if ((long long)round * G >= n_items) return -1;
+        const long long t = (round & 1) ? (long long)(round + 1) * G - 1 - c : (long long)round * G + c;
+        if (t >= n_items) return 0;
+        const int4 ti = tiles[t / n_q];
+        it.slot = ti.x, it.row0 = ti.y, it.n_rows = ti.z, it.pos0 = ti.w;
+        it.h = (int)(t % n_q), it.kvh = it.h / (n_q / n_kv);
+        const int hi = it.pos0 + it.n_rows - 1;
+        const int lo = window > 0 ? max(0, it.pos0 - window + 1) : 0;
+        it.kt_lo = lo / FT_BN;
+        it.n_tiles = (it.slot < 0 || it.n_rows <= 0) ? 0 : hi / FT_BN - it.kt_lo + 1;
+        return it.n_tiles > 0 ? 1 : 0;
+    };
     volatile int* abort = &ctl->abort;
 
     if (threadIdx.x == 0) {
         ft_mbar_init(&ctl->q_full, 1);
+        ft_mbar_init(&ctl->q_empty, 1);
+        ft_mbar_init(&ctl->o_free, 4);
         for (int s = 0; s < FT_STAGES; ++s) {
             ft_mbar_init(&ctl->k_full[s], 1); ft_mbar_init(&ctl->k_empty[s], 1);
             ft_mbar_init(&ctl->v_full[s], 1); ft_mbar_init(&ctl->v_empty[s], 1);
@@ -190,44 +208,57 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __
     const uint32_t tmem = ctl->tmem_base;
 
     if (warp == 0) {
-        if (lane == 0 && n_tiles > 0) {
-            ft_mbar_expect_tx(&ctl->q_full, FT_Q_BYTES);
-            ft_tma_load_2d(q_tile, &map_q, h * FT_D, row0, &ctl->q_full);
-            ft_tma_load_2d(q_tile + FT_Q_BYTES / 2, &map_q, h * FT_D + 64, row0, &ctl->q_full);
-            const int* bt_row = block_table + (size_t)slot * max_pages;
+        if (lane == 0) {
             // Keys and values have rings of their own: the keys of a tile are free again as soon as its
             // scores are computed (a tile ahead of the softmax), the values only after P V.  Keys of tile
             // it + 1 go out before the values of tile it, in the order in which the stages come free.
-            auto tile_row = [&](int it) {
-                const int key0 = (kt_lo + it) * FT_BN;
-                const int lp = key0 / page_size;
-                int page = lp < max_pages ? bt_row[lp] : -1;
-                if (page < 0 || page >= n_pool_pages) { atomicExch(error_flag, FT_ERR_PAGE); page = 0; }
-                return (page * n_kv + kvh) * page_size + (key0 - lp * page_size);
-            };
-            int armed_k = 0, armed_v = 0;
-            auto load = [&](int it, bool keys) -> bool {
-                const int s = it % FT_STAGES;
-                unsigned long long* empty = keys ? &ctl->k_empty[s] : &ctl->v_empty[s];
-                unsigned long long* full = keys ? &ctl->k_full[s] : &ctl->v_full[s];
-                if (!ft_mbar_wait(empty, ((it / FT_STAGES) & 1) ^ 1, abort)) return false;
-                const int row = tile_row(it);
-                unsigned char* dst = (keys ? k_tiles : v_tiles) + s * FT_KV_BYTES;
-                ft_mbar_expect_tx(full, FT_KV_BYTES);
-                ft_tma_load_2d(dst, keys ? &map_k : &map_v, 0, row, full);
-                ft_tma_load_2d(dst + FT_KV_BYTES / 2, keys ? &map_k : &map_v, 64, row, full);
-                (keys ? armed_k : armed_v) = it + 1;
-                return true;
-            };
-            bool ok = load(0, true);
-            for (int it = 0; it < n_tiles && ok; ++it) {
-                if (it + 1 < n_tiles) ok = load(it + 1, true);
-                if (ok) ok = load(it, false);
+            int qn = 0, g0 = 0;                          // items and key tiles done so far: the barriers' phases go on
+            int armed_q = 0, armed_k = 0, armed_v = 0;
+            bool ok = true;
+            FtItem im;
+            for (int round = 0; ok; ++round) {
+                const int have = item_at(round, im);
+                if (have < 0) break;
+                if (have == 0) continue;
+                // the query tile may be overwritten when the last scores of the item before are computed
+                if (!ft_mbar_wait(&ctl->q_empty, (qn & 1) ^ 1, abort)) { ok = false; break; }
+                ft_mbar_expect_tx(&ctl->q_full, FT_Q_BYTES);
+                ft_tma_load_2d(q_tile, &map_q, im.h * FT_D, im.row0, &ctl->q_full);
+                ft_tma_load_2d(q_tile + FT_Q_BYTES / 2, &map_q, im.h * FT_D + 64, im.row0, &ctl->q_full);
+                armed_q = qn + 1;
+                const int* bt_row = block_table + (size_t)im.slot * max_pages;
+                auto tile_row = [&](int it) {
+                    const int key0 = (im.kt_lo + it) * FT_BN;
+                    const int lp = key0 / page_size;
+                    int page = lp < max_pages ? bt_row[lp] : -1;
+                    if (page < 0 || page >= n_pool_pages) { atomicExch(error_flag, FT_ERR_PAGE); page = 0; }
+                    return (page * n_kv + im.kvh) * page_size + (key0 - lp * page_size);
+                };
+                auto load = [&](int it, bool keys) -> bool {
+                    const int g = g0 + it, s = g % FT_STAGES;
+                    unsigned long long* empty = keys ? &ctl->k_empty[s] : &ctl->v_empty[s];
+                    unsigned long long* full = keys ? &ctl->k_full[s] : &ctl->v_full[s];
+                    if (!ft_mbar_wait(empty, ((g / FT_STAGES) & 1) ^ 1, abort)) return false;
+                    const int row = tile_row(it);
+                    unsigned char* dst = (keys ? k_tiles : v_tiles) + s * FT_KV_BYTES;
+                    ft_mbar_expect_tx(full, FT_KV_BYTES);
+                    ft_tma_load_2d(dst, keys ? &map_k : &map_v, 0, row, full);
+                    ft_tma_load_2d(dst + FT_KV_BYTES / 2, keys ? &map_k : &map_v, 64, row, full);
+                    (keys ? armed_k : armed_v) = g + 1;
+                    return true;
+                };
+                ok = load(0, true);
+                for (int it = 0; it < im.n_tiles && ok; ++it) {
+                    if (it + 1 < im.n_tiles) ok = load(it + 1, true);
+                    if (ok) ok = load(it, false);
+                }
+                g0 += im.n_tiles;
+                ++qn;
             }
             if (!ok && !*abort) { *abort = 1; atomicExch(error_flag, FT_ERR_PRODUCER); }
             if (*abort) {                                // no copy may be in flight when the CTA leaves
                 int never = 0;
-                ft_mbar_wait(&ctl->q_full, 0, &never);
+                if (armed_q > 0) ft_mbar_wait(&ctl->q_full, (armed_q - 1) & 1, &never);
                 for (int i = max(0, armed_k - FT_STAGES); i < armed_k; ++i)
                     ft_mbar_wait(&ctl->k_full[i % FT_STAGES], (i / FT_STAGES) & 1, &never);
                 for (int i = max(0, armed_v - FT_STAGES); i < armed_v; ++i)
@@ -235,139 +266,155 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __
             }
         }
     } else if (warp == 1) {
-        if (lane == 0 && n_tiles > 0) {
+        if (lane == 0) {
             // S = Q K^T: float32 accumulate, bfloat16 operands, both K-major, N = 64, M = 128
             const uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(FT_BN >> 3) << 17) | ((uint32_t)(FT_BM >> 4) << 24);
             // P V: the same with the second operand MN-major (bit 16), N = 128
             const uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(FT_D >> 3) << 17) | ((uint32_t)(FT_BM >> 4) << 24);
             const uint32_t q_addr = ft_smem(q_tile);
-            bool ok = ft_mbar_wait(&ctl->q_full, 0, abort);
-            if (!ok && !*abort) { *abort = 1; atomicExch(error_flag, FT_ERR_MMA); }
-            auto issue_s = [&](int it) -> bool {
-                const int s = it % FT_STAGES;
-                if (!ft_mbar_wait(&ctl->k_full[s], (it / FT_STAGES) & 1, abort)) return false;
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t k_addr = ft_smem(k_tiles + s * FT_KV_BYTES);
+            int qn = 0, g0 = 0;
+            bool ok = true;
+            FtItem im;
+            for (int round = 0; ok; ++round) {
+                const int have = item_at(round, im);
+                if (have < 0) break;
+                if (have == 0) continue;
+                if (!ft_mbar_wait(&ctl->q_full, qn & 1, abort)) { ok = false; break; }
+                auto issue_s = [&](int it) -> bool {
+                    const int g = g0 + it, s = g % FT_STAGES;
+                    if (!ft_mbar_wait(&ctl->k_full[s], (g / FT_STAGES) & 1, abort)) return false;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t k_addr = ft_smem(k_tiles + s * FT_KV_BYTES);
 #pragma unroll
-                for (int k = 0; k < FT_D / 16; ++k) {
-                    const uint32_t qa = q_addr + (k >> 2) * (FT_Q_BYTES / 2) + (k & 3) * 32;
-                    const uint32_t ka = k_addr + (k >> 2) * (FT_KV_BYTES / 2) + (k & 3) * 32;
-                    ft_mma_ss(tmem + FT_COL_S + (it & 1) * FT_BN, ft_desc_kmajor(qa), ft_desc_kmajor(ka), idesc_s, k != 0);
+                    for (int k = 0; k < FT_D / 16; ++k) {
+                        const uint32_t qa = q_addr + (k >> 2) * (FT_Q_BYTES / 2) + (k & 3) * 32;
+                        const uint32_t ka = k_addr + (k >> 2) * (FT_KV_BYTES / 2) + (k & 3) * 32;
+                        ft_mma_ss(tmem + FT_COL_S + (g & 1) * FT_BN, ft_desc_kmajor(qa), ft_desc_kmajor(ka), idesc_s, k != 0);
+                    }
+                    ft_commit(&ctl->s_full[g & 1]);
+                    ft_commit(&ctl->k_empty[s]);
+                    if (it + 1 == im.n_tiles) ft_commit(&ctl->q_empty);      // the item's last scores: the query tile is free
+                    return true;
+                };
+                ok = issue_s(0);
+                for (int it = 0; it < im.n_tiles && ok; ++it) {
+                    const int g = g0 + it, s = g % FT_STAGES;
+                    // The scores of the next tile, into the other buffer, while the softmax warps work on this
+                    // one.  The products run in the order they are issued, so this one starts after P V of the
+                    // tile before, which read its probabilities from that buffer.
+                    if (it + 1 < im.n_tiles && !(ok = issue_s(it + 1))) break;
+                    if (!ft_mbar_wait(&ctl->p_ready[g & 1], (g >> 1) & 1, abort) ||
+                        !ft_mbar_wait(&ctl->v_full[s], (g / FT_STAGES) & 1, abort)) { ok = false; break; }
+                    // the first P V of an item overwrites O: the softmax warps have read the item before out of it
+                    if (it == 0 && !ft_mbar_wait(&ctl->o_free, (qn & 1) ^ 1, abort)) { ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t v_addr = ft_smem(v_tiles + s * FT_KV_BYTES);
+#pragma unroll
+                    for (int k = 0; k < FT_BN / 16; ++k)     // 16 keys = two groups of 8 rows = 2,048 bytes further
+                        ft_mma_ts(tmem + FT_COL_O, tmem + FT_COL_S + (g & 1) * FT_BN + k * 8,
+                                  ft_desc_mnmajor(v_addr + k * 2048, FT_KV_BYTES / 2), idesc_o, (it | k) != 0);
+                    ft_commit(&ctl->o_done);
+                    ft_commit(&ctl->v_empty[s]);
                 }
-                ft_commit(&ctl->s_full[it & 1]);
-                ft_commit(&ctl->k_empty[s]);
-                return true;
-            };
-            if (ok) ok = issue_s(0);
-            for (int it = 0; it < n_tiles && ok; ++it) {
-                const int s = it % FT_STAGES;
-                // The scores of the next tile, into the other buffer, while the softmax warps work on this
-                // one.  The products run in the order they are issued, so this one starts after P V of the
-                // tile before, which read its probabilities from that buffer.
-                if (it + 1 < n_tiles && !(ok = issue_s(it + 1))) break;
-                if (!ft_mbar_wait(&ctl->p_ready[it & 1], (it >> 1) & 1, abort) ||
-                    !ft_mbar_wait(&ctl->v_full[s], (it / FT_STAGES) & 1, abort)) { ok = false; break; }
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t v_addr = ft_smem(v_tiles + s * FT_KV_BYTES);
-#pragma unroll
-                for (int k = 0; k < FT_BN / 16; ++k)     // 16 keys = two groups of 8 rows = 2,048 bytes further
-                    ft_mma_ts(tmem + FT_COL_O, tmem + FT_COL_S + (it & 1) * FT_BN + k * 8,
-                              ft_desc_mnmajor(v_addr + k * 2048, FT_KV_BYTES / 2), idesc_o, (it | k) != 0);
-                ft_commit(&ctl->o_done);
-                ft_commit(&ctl->v_empty[s]);
+                g0 += im.n_tiles;
+                ++qn;
             }
             if (!ok && !*abort) { *abort = 1; atomicExch(error_flag, FT_ERR_MMA); }
         }
-    } else if (n_tiles > 0) {
+    } else {
         const int q = warp & 3;
         const int r = q * 32 + lane;                     // this thread's query row = its lane of tensor memory
-        const int pos = pos0 + r;
         const uint32_t lane_base = tmem + ((uint32_t)(q * 32) << 16);
-        float ref = -INFINITY, l = 0.f;                  // exponentials are taken against `ref`; l is the sum of them
         bool ok = true;
         // tensor memory is read and written by whole warps: a wait that gives up does so for the whole warp
         auto wait_warp = [&](void* bar, uint32_t parity) {
             const bool w = ft_mbar_wait(bar, parity, abort);
             return __all_sync(0xffffffffu, w);
         };
-        for (int it = 0; it < n_tiles; ++it) {
-            const int b = it & 1;
-            if (!wait_warp(&ctl->s_full[b], (it >> 1) & 1)) { ok = false; break; }
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const int key0 = (kt_lo + it) * FT_BN;
-            float s[FT_BN];                              // raw scores: the scale is folded into the exponent below
-            {
-                float a[32], c[32];
-                ft_ld32(lane_base + FT_COL_S + b * FT_BN, a);
-                ft_ld32(lane_base + FT_COL_S + b * FT_BN + 32, c);
+        int g0 = 0;
+        FtItem im;
+        for (int round = 0; ok; ++round) {
+            const int have = item_at(round, im);
+            if (have < 0) break;
+            if (have == 0) continue;
+            const int pos = im.pos0 + r;
+            float ref = -INFINITY, l = 0.f;              // exponentials are taken against `ref`; l is the sum of them
+            for (int it = 0; it < im.n_tiles; ++it) {
+                const int g = g0 + it, b = g & 1;
+                if (!wait_warp(&ctl->s_full[b], (g >> 1) & 1)) { ok = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const int key0 = (im.kt_lo + it) * FT_BN;
+                float s[FT_BN];                          // raw scores: the scale is folded into the exponent below
+                {
+                    float a[32], c2[32];
+                    ft_ld32(lane_base + FT_COL_S + b * FT_BN, a);
+                    ft_ld32(lane_base + FT_COL_S + b * FT_BN + 32, c2);
 #pragma unroll
-                for (int j = 0; j < 32; ++j) { s[j] = a[j]; s[32 + j] = c[j]; }
-            }
-            // tiles that every row of the CTA sees whole need no mask
-            if (key0 + FT_BN - 1 > pos0 || (window > 0 && key0 <= pos0 + FT_BM - 1 - window)) {
-#pragma unroll
-                for (int j = 0; j < FT_BN; ++j) {
-                    const int key = key0 + j;
-                    const bool seen = key <= pos && (window <= 0 || key > pos - window);
-                    s[j] = seen ? s[j] : -INFINITY;
+                    for (int j = 0; j < 32; ++j) { s[j] = a[j]; s[32 + j] = c2[j]; }
                 }
-            }
-            float mx4[4] = {s[0], s[1], s[2], s[3]};     // four chains instead of one of 63 dependent steps
+                // tiles that every row of the CTA sees whole need no mask
+                if (key0 + FT_BN - 1 > im.pos0 || (window > 0 && key0 <= im.pos0 + FT_BM - 1 - window)) {
 #pragma unroll
-            for (int j = 4; j < FT_BN; ++j) mx4[j & 3] = fmaxf(mx4[j & 3], s[j]);
-            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;   // the scale is positive
-            if (it == 0) {
-                ref = mx;                                // nothing accumulated yet: nothing to rescale
-            } else {
-                // O must not change under the rescale: P V of the tile before has to be done (it has been
-                // for long, as a rule).  Waited for every tile, so that the barrier's phases are seen in order.
-                if (!wait_warp(&ctl->o_done, (it - 1) & 1)) { ok = false; break; }
-                const bool grow = mx > ref + FT_LAZY;    // also a row that sees its first key (ref = -inf)
-                if (__any_sync(0xffffffffu, grow)) {     // tensor memory is read and written by whole warps
-                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const float corr = grow ? exp2f(ref - mx) : 1.f;
-#pragma unroll
-                    for (int c4 = 0; c4 < FT_D / 32; ++c4) {
-                        float o[32];
-                        uint32_t u[32];
-                        ft_ld32(lane_base + FT_COL_O + c4 * 32, o);
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) u[j] = __float_as_uint(o[j] * corr);
-                        ft_st32(lane_base + FT_COL_O + c4 * 32, u);
+                    for (int j = 0; j < FT_BN; ++j) {
+                        const int key = key0 + j;
+                        const bool seen = key <= pos && (window <= 0 || key > pos - window);
+                        s[j] = seen ? s[j] : -INFINITY;
                     }
-                    l *= corr;
-                    if (grow) ref = mx;
                 }
-            }
-            const float neg_use = ref == -INFINITY ? 0.f : -ref;     // a row that has seen no key yet stays all zero
-            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-            uint32_t pk[32];
+                float mx4[4] = {s[0], s[1], s[2], s[3]}; // four chains instead of one of 63 dependent steps
 #pragma unroll
-            for (int j = 0; j < FT_BN; j += 2) {
-                // one multiply-add and one ex2 per score; results below 2^-126 are flushed to zero
-                const float p0 = ft_ex2(fmaf(s[j], scale_log2, neg_use)), p1 = ft_ex2(fmaf(s[j + 1], scale_log2, neg_use));
-                sum4[(j >> 1) & 3] += p0 + p1;
-                __nv_bfloat162 v = __floats2bfloat162_rn(p0, p1);
-                pk[j >> 1] = *reinterpret_cast<uint32_t*>(&v);
+                for (int j = 4; j < FT_BN; ++j) mx4[j & 3] = fmaxf(mx4[j & 3], s[j]);
+                const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;   // the scale is positive
+                if (it == 0) {
+                    ref = mx;                            // nothing accumulated yet: nothing to rescale
+                } else {
+                    // O must not change under the rescale: P V of the tile before has to be done (it has been
+                    // for long, as a rule).  Waited for every tile, so that the barrier's phases are seen in order.
+                    if (!wait_warp(&ctl->o_done, (g - 1) & 1)) { ok = false; break; }
+                    const bool grow = mx > ref + FT_LAZY;    // also a row that sees its first key (ref = -inf)
+                    if (__any_sync(0xffffffffu, grow)) { // tensor memory is read and written by whole warps
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        const float corr = grow ? exp2f(ref - mx) : 1.f;
+#pragma unroll
+                        for (int c4 = 0; c4 < FT_D / 32; ++c4) {
+                            float o[32];
+                            uint32_t u[32];
+                            ft_ld32(lane_base + FT_COL_O + c4 * 32, o);
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) u[j] = __float_as_uint(o[j] * corr);
+                            ft_st32(lane_base + FT_COL_O + c4 * 32, u);
+                        }
+                        l *= corr;
+                        if (grow) ref = mx;
+                    }
+                }
+                const float neg_use = ref == -INFINITY ? 0.f : -ref; // a row that has seen no key yet stays all zero
+                float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+                uint32_t pk[32];
+#pragma unroll
+                for (int j = 0; j < FT_BN; j += 2) {
+                    // one multiply-add and one ex2 per score; results below 2^-126 are flushed to zero
+                    const float p0 = ft_ex2(fmaf(s[j], scale_log2, neg_use)), p1 = ft_ex2(fmaf(s[j + 1], scale_log2, neg_use));
+                    sum4[(j >> 1) & 3] += p0 + p1;
+                    __nv_bfloat162 v = __floats2bfloat162_rn(p0, p1);
+                    pk[j >> 1] = *reinterpret_cast<uint32_t*>(&v);
+                }
+                l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+                ft_st32(lane_base + FT_COL_S + b * FT_BN, pk);
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) ft_mbar_arrive(&ctl->p_ready[b]);
             }
-            const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-            l += sum;
-            ft_st32(lane_base + FT_COL_S + b * FT_BN, pk);
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) ft_mbar_arrive(&ctl->p_ready[b]);
-        }
-        if (ok && !wait_warp(&ctl->o_done, (n_tiles - 1) & 1)) ok = false;
-        if (!ok && !*abort) { *abort = 1; atomicExch(error_flag, FT_ERR_SOFTMAX); }
-        if (ok) {
+            if (ok && !wait_warp(&ctl->o_done, (g0 + im.n_tiles - 1) & 1)) ok = false;
+            if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const float inv = l > 0.f ? 1.f / l : 0.f;
-            bf16* dst = out + ((size_t)(row0 + r) * n_q + h) * FT_D;
+            bf16* dst = out + ((size_t)(im.row0 + r) * n_q + im.h) * FT_D;
 #pragma unroll
             for (int c4 = 0; c4 < FT_D / 32; ++c4) {
                 float o[32];
                 ft_ld32(lane_base + FT_COL_O + c4 * 32, o);      // by whole warps, rows beyond the tile too
-                if (r < n_rows) {
+                if (r < im.n_rows) {
 #pragma unroll
                     for (int i = 0; i < 32; i += 8) {
                         uint4 v;
@@ -381,7 +428,13 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __
                     }
                 }
             }
+            // O is in registers: the first P V of the next item may overwrite it
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) ft_mbar_arrive(&ctl->o_free);
+            g0 += im.n_tiles;
         }
+        if (!ok && !*abort) { *abort = 1; atomicExch(error_flag, FT_ERR_SOFTMAX); }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
@@ -449,8 +502,15 @@ extern "C" int gi_attention_prefill_tcgen05(const void* q, const void* k_pool, c
         if (e != cudaSuccess) { gi_set_error("gi_attention_prefill_tcgen05: shared memory: %s", cudaGetErrorString(e)); return (int)e; }
         attr_done = true;
     }
-    gi_launch(flash_prefill_tcgen05_kernel, dim3(n_tiles, n_q), dim3(FT_THREADS), smem, (cudaStream_t)stream, map_q, map_k,
-              map_v, block_table, (const int4*)tiles, (bf16*)out, n_q, n_kv, page_size, max_pages, n_pool_pages, window,
-              scale * 1.4426950408889634f, error_flag);
+    int n_sm = 148;
+    {
+        int dev = 0;
+        if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
+    }
+    const long long items = (long long)n_tiles * n_q;
+    const long long grid = items < 2LL * n_sm ? items : 2LL * n_sm;      // two CTAs fit an SM
+    gi_launch(flash_prefill_tcgen05_kernel, dim3((unsigned)grid), dim3(FT_THREADS), smem, (cudaStream_t)stream, map_q, map_k,
+              map_v, block_table, (const int4*)tiles, n_tiles, (bf16*)out, n_q, n_kv, page_size, max_pages, n_pool_pages,
+              window, scale * 1.4426950408889634f, error_flag);
     return gi_check_launch("gi_attention_prefill_tcgen05");
 }
