@@ -4,6 +4,8 @@ Which product runs:
   * float32 weight: this package's own float32 FMA kernel (no tensor-core or
     reduced-precision mode); bfloat16 activations are widened first and the
     result narrowed again.
+  * bfloat16 weight of 256 MB and more (the head), 1 to 16 rows: this package's
+    stream-K tcgen05 kernel, which cuts the weight evenly over the SMs.
   * bfloat16 weight, one row: this package's bandwidth kernel (GEMV).
   * bfloat16 weight, 2 to 8 rows: this package's tensor-core kernel for
     decode batches, which reads the weight once.
@@ -11,6 +13,8 @@ Which product runs:
     `torch.mm`), float32 accumulation, or this package's tcgen05 kernel when
     `LARGE_GEMM` says so.  Upstream uses the same library for all
     its products (src/src-cuda/mat-ops/gemm/gemm.cu:22-41).
+`swiglu_product` is the gate/up product of a SwiGLU feed-forward with its activation: one
+tcgen05 kernel for prompts, product and SwiGLU kernel otherwise.
 """
 from __future__ import annotations
 
@@ -24,7 +28,7 @@ from .library import KernelError
 
 # Which product takes bfloat16 weights with more than SKINNY_MAX_ROWS rows of x: "library" (cuBLAS through
 # torch.mm) or "tcgen05" (this package's TMA/tcgen05 kernel).  Measured at 2,048 rows and Qwen3-8B sizes the
-# library runs 1.43-1.53 PFLOP/s and the tcgen05 kernel 1.09-1.27, so the library is the default; set
+# library runs 1.43-1.55 PFLOP/s and the tcgen05 kernel 1.26-1.40 (pairs of CTAs), so the library is the default; set
 # GARLIC_B200_GEMM=tcgen05 (or this variable) to run this package's kernel instead.
 LARGE_GEMM = os.environ.get("GARLIC_B200_GEMM", "library")
 
@@ -33,12 +37,13 @@ LARGE_GEMM = os.environ.get("GARLIC_B200_GEMM", "library")
 # against 276 us for the library product plus 33 us for the SwiGLU kernel.  0 switches it off.
 FUSED_SWIGLU_MIN_ROWS = int(os.environ.get("GARLIC_B200_FUSED_SWIGLU_ROWS", "512"))
 
-# Which kernel takes bfloat16 products of 1 to 8 rows whose weight has at least this many bytes: the stream-K
+# Which kernel takes bfloat16 products of 1 to 16 rows whose weight has at least this many bytes: the stream-K
 # tcgen05 kernel (W cut evenly over the SMs, 6.6 TB/s once it runs but about 10 us to start and to merge the
 # cut tiles).  Measured at 8 rows: 189 against 216 us on the 1.24 GB head, 39.4 against 38.9 us on 201 MB,
 # 27.8 against 22.8 us on 101 MB; so smaller weights stay with the gemv / skinny kernels.  0 switches it off.
 STREAMK_MIN_BYTES = int(os.environ.get("GARLIC_B200_STREAMK_MIN_BYTES", str(256 << 20)))
 
+STREAMK_MAX_ROWS = 16
 GEMV_MAX_ROWS = 1          # one row: the plain bandwidth kernel
 SKINNY_MAX_ROWS = 8        # up to here: the tensor-core kernel that streams W once (it takes 16; the library is faster from 9 on)
 
@@ -57,9 +62,10 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
     m, k = x.shape
     if m == 0:
         return torch.empty((0, w.shape[0]), dtype=out_dtype, device=x.device)
-    if m <= SKINNY_MAX_ROWS and k % 8 == 0 and w.data_ptr() % 16 == 0 and x.data_ptr() % 16 == 0:
-        if 0 < STREAMK_MIN_BYTES <= w.numel() * 2:
-            return kernels.gemm_streamk_bf16(x, w, out_dtype)
+    aligned = k % 8 == 0 and w.data_ptr() % 16 == 0 and x.data_ptr() % 16 == 0
+    if m <= STREAMK_MAX_ROWS and aligned and 0 < STREAMK_MIN_BYTES <= w.numel() * 2:
+        return kernels.gemm_streamk_bf16(x, w, out_dtype)
+    if m <= SKINNY_MAX_ROWS and aligned:
         if m <= GEMV_MAX_ROWS:
             return kernels.gemv_bf16(x, w, out_dtype)
         return kernels.gemm_skinny_bf16(x, w, out_dtype)
