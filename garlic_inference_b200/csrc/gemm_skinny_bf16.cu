@@ -60,7 +60,11 @@ __device__ __forceinline__ void sk_step(float (&acc)[NT][4], const uint4& lo0, c
     }
 }
 
-template <int NT, int WR, int WK>
+// GLU: W is [2 I, K], a gate projection in its first I rows and an up projection in its last I.  A CTA then
+// takes R / 2 gate rows and the R / 2 up rows that belong to them, and writes silu(gate) * up, [M, I]
+// bfloat16: each factor rounded to bfloat16 as a stored product would be, then the SwiGLU kernel's float32
+// arithmetic, so the result has the bits of the product followed by that kernel.
+template <int NT, int WR, int WK, bool GLU>
 __global__ void __launch_bounds__(SK_THREADS)
 skinny_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, void* __restrict__ out, int out_f32,
                    int M, int N, int K, int k_slice) {
@@ -80,8 +84,16 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, void*
     const int row0 = blockIdx.x * R;
     const int k_begin = blockIdx.y * k_slice, k_end = min(K, k_begin + k_slice);
 
-    const bf16* wa = W + (size_t)min(row0 + wr * 16 + g, N - 1) * K;
-    const bf16* wb = W + (size_t)min(row0 + wr * 16 + g + 8, N - 1) * K;
+    // the rows of W behind local rows wr * 16 + g and + 8
+    auto w_row = [&](int local) {
+        if (!GLU) return min(row0 + local, N - 1);
+        constexpr int half = R / 2;
+        const int inter = N / 2;
+        return local < half ? min((int)blockIdx.x * half + local, inter - 1)
+                            : min(inter + (int)blockIdx.x * half + local - half, N - 1);
+    };
+    const bf16* wa = W + (size_t)w_row(wr * 16 + g) * K;
+    const bf16* wb = W + (size_t)w_row(wr * 16 + g + 8) * K;
     const bf16* xr[NT];
     bool xok[NT];
 #pragma unroll
@@ -165,35 +177,56 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, void*
     const unsigned n_ranks = cluster.num_blocks(), rank = cluster.block_rank();
     if (n_ranks > 1) cluster.sync(); else __syncthreads();
     // every CTA of the cluster finishes one share of the tile, adding the partials in rank order
-    const int share = (MP * R + n_ranks - 1) / n_ranks;
-    const int i_end = min(MP * R, (int)(rank + 1) * share);
-    for (int i = rank * share + threadIdx.x; i < i_end; i += SK_THREADS) {
-        float v = 0.f;
-        for (unsigned c = 0; c < n_ranks; ++c) v += n_ranks > 1 ? cluster.map_shared_rank(part, c)[i] : part[i];
-        const int m = i / R, row = row0 + i % R;
-        if (m < M && row < N) {
-            if (out_f32) reinterpret_cast<float*>(out)[(size_t)m * N + row] = v;
-            else reinterpret_cast<bf16*>(out)[(size_t)m * N + row] = __float2bfloat16_rn(v);
+    if (GLU) {
+        constexpr int half = R / 2;
+        const int inter = N / 2;
+        const int share = (MP * half + n_ranks - 1) / n_ranks;
+        const int i_end = min(MP * half, (int)(rank + 1) * share);
+        for (int i = rank * share + threadIdx.x; i < i_end; i += SK_THREADS) {
+            const int m = i / half, r = i % half;
+            float gate = 0.f, up = 0.f;
+            for (unsigned c = 0; c < n_ranks; ++c) {
+                const float* p = n_ranks > 1 ? cluster.map_shared_rank(part, c) : part;
+                gate += p[m * R + r];
+                up += p[m * R + r + half];
+            }
+            const int col = blockIdx.x * half + r;
+            if (m < M && col < inter) {
+                const float gf = __bfloat162float(__float2bfloat16_rn(gate)), uf = __bfloat162float(__float2bfloat16_rn(up));
+                reinterpret_cast<bf16*>(out)[(size_t)m * inter + col] = __float2bfloat16_rn(gf / (1.f + expf(-gf)) * uf);
+            }
+        }
+    } else {
+        const int share = (MP * R + n_ranks - 1) / n_ranks;
+        const int i_end = min(MP * R, (int)(rank + 1) * share);
+        for (int i = rank * share + threadIdx.x; i < i_end; i += SK_THREADS) {
+            float v = 0.f;
+            for (unsigned c = 0; c < n_ranks; ++c) v += n_ranks > 1 ? cluster.map_shared_rank(part, c)[i] : part[i];
+            const int m = i / R, row = row0 + i % R;
+            if (m < M && row < N) {
+                if (out_f32) reinterpret_cast<float*>(out)[(size_t)m * N + row] = v;
+                else reinterpret_cast<bf16*>(out)[(size_t)m * N + row] = __float2bfloat16_rn(v);
+            }
         }
     }
     if (n_ranks > 1) cluster.sync();            // nobody leaves while a peer still reads its partial
 }
 
-template <int NT, int WR, int WK>
+template <int NT, int WR, int WK, bool GLU>
 static int launch_skinny(const bf16* x, const bf16* W, void* out, int out_f32, int M, int N, int K, int n_split,
                          cudaStream_t stream) {
     constexpr int MP = 8 * NT, R = 16 * WR, KC = 64 * WK;
     const size_t smem = (size_t)SK_DEPTH * 4 * SK_THREADS * 16 + (size_t)(WK + 1) * MP * R * sizeof(float);
     static bool attr_done = false;
     if (!attr_done) {
-        cudaError_t e = cudaFuncSetAttribute((const void*)skinny_gemm_kernel<NT, WR, WK>,
+        cudaError_t e = cudaFuncSetAttribute((const void*)skinny_gemm_kernel<NT, WR, WK, GLU>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) { gi_set_error("gi_gemm_skinny_bf16: shared memory: %s", cudaGetErrorString(e)); return (int)e; }
         attr_done = true;
     }
     const int k_slice = ((K + n_split - 1) / n_split + KC - 1) / KC * KC;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((N + R - 1) / R, n_split, 1);
+    cfg.gridDim = dim3(GLU ? (N / 2 + R / 2 - 1) / (R / 2) : (N + R - 1) / R, n_split, 1);
     cfg.blockDim = dim3(SK_THREADS, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
@@ -206,28 +239,31 @@ static int launch_skinny(const bf16* x, const bf16* W, void* out, int out_f32, i
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = gi_pdl_enabled() ? 2 : 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, skinny_gemm_kernel<NT, WR, WK>, x, W, out, out_f32, M, N, K, k_slice);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, skinny_gemm_kernel<NT, WR, WK, GLU>, x, W, out, out_f32, M, N, K, k_slice);
     if (e != cudaSuccess) { gi_set_error("gi_gemm_skinny_bf16: launch: %s", cudaGetErrorString(e)); return (int)e; }
     return gi_check_launch("gi_gemm_skinny_bf16");
 }
 
 // n_split: CTAs of a cluster that share K (1 to 8); 0 lets the entry point choose.
 // wide: 0 = 32 rows of W per CTA, 1 = 64 rows, -1 lets the entry point choose.
-extern "C" int gi_gemm_skinny_bf16(const void* x, const void* W, void* out, int out_dtype, int M, int N, int K,
-                                   int n_split, int wide, void* stream) {
+// glu: 0 = out[M, N]; 1 = W holds a gate and an up half and out is silu(gate) * up, [M, N / 2] bfloat16.
+static int skinny_entry(const void* x, const void* W, void* out, int out_dtype, int M, int N, int K, int n_split,
+                        int wide, int glu, void* stream) {
     GI_REQUIRE(M >= 1 && M <= 16, "gi_gemm_skinny_bf16: %d rows; this kernel takes 1 to 16", M);
     GI_REQUIRE(N > 0 && K > 0 && K % 8 == 0, "gi_gemm_skinny_bf16: inner size %d must be a positive multiple of 8", K);
     GI_REQUIRE(((uintptr_t)x % 16 == 0) && ((uintptr_t)W % 16 == 0), "gi_gemm_skinny_bf16: operands must start on 16 bytes");
     GI_REQUIRE(out_dtype == GI_DTYPE_BF16 || out_dtype == GI_DTYPE_F32, "gi_gemm_skinny_bf16: output dtype %d", out_dtype);
     GI_REQUIRE(n_split >= 0 && n_split <= 8, "gi_gemm_skinny_bf16: a cluster of %d CTAs; 1 to 8 are possible", n_split);
     GI_REQUIRE(wide >= -1 && wide <= 1, "gi_gemm_skinny_bf16: wide must be -1, 0 or 1");
+    GI_REQUIRE(!glu || (N % 2 == 0 && out_dtype == GI_DTYPE_BF16),
+               "gi_gemm_skinny_swiglu_bf16: W must hold a gate and an up half (%d rows) and the output be bfloat16", N);
     // Every CTA streams at the pace its own loads in flight allow, so the launch should fit the GPU in one
     // wave of equal CTAs (3 fit an SM) or be many waves long.
     const int slots = 148 * 3;
     if (wide < 0) wide = (N + 31) / 32 > slots && (N + 63) / 64 <= 8 * slots ? 1 : 0;
     const int R = wide ? 64 : 32, KC = wide ? 128 : 256;
     if (n_split == 0) {
-        const long long tiles = (N + R - 1) / R;
+        const long long tiles = glu ? (N / 2 + R / 2 - 1) / (R / 2) : (N + R - 1) / R;
         n_split = 1;
         while (n_split < 8 && tiles * (n_split + 1) <= slots && K / (n_split + 1) >= 2 * KC) ++n_split;
     }
@@ -235,8 +271,21 @@ extern "C" int gi_gemm_skinny_bf16(const void* x, const void* W, void* out, int 
     const bf16* wp = (const bf16*)W;
     const int f32 = out_dtype == GI_DTYPE_F32;
     cudaStream_t s = (cudaStream_t)stream;
-    if (M <= 8) return wide ? launch_skinny<1, 4, 2>(xp, wp, out, f32, M, N, K, n_split, s)
-                            : launch_skinny<1, 2, 4>(xp, wp, out, f32, M, N, K, n_split, s);
-    return wide ? launch_skinny<2, 4, 2>(xp, wp, out, f32, M, N, K, n_split, s)
-                : launch_skinny<2, 2, 4>(xp, wp, out, f32, M, N, K, n_split, s);
+#define GI_SK(NT, WR, WK) (glu ? launch_skinny<NT, WR, WK, true>(xp, wp, out, f32, M, N, K, n_split, s) \
+                               : launch_skinny<NT, WR, WK, false>(xp, wp, out, f32, M, N, K, n_split, s))
+    if (M <= 8) return wide ? GI_SK(1, 4, 2) : GI_SK(1, 2, 4);
+    return wide ? GI_SK(2, 4, 2) : GI_SK(2, 2, 4);
+#undef GI_SK
+}
+
+extern "C" int gi_gemm_skinny_bf16(const void* x, const void* W, void* out, int out_dtype, int M, int N, int K,
+                                   int n_split, int wide, void* stream) {
+    return skinny_entry(x, W, out, out_dtype, M, N, K, n_split, wide, 0, stream);
+}
+
+// out[M, I] = silu(x . Wg^T) * (x . Wu^T) for W = [Wg; Wu] of two_inter = 2 I rows: the gate/up product of a
+// SwiGLU feed-forward at decode batches with the activation in the kernel's last step.
+extern "C" int gi_gemm_skinny_swiglu_bf16(const void* x, const void* W, void* out, int M, int two_inter, int K,
+                                          int n_split, int wide, void* stream) {
+    return skinny_entry(x, W, out, GI_DTYPE_BF16, M, two_inter, K, n_split, wide, 1, stream);
 }

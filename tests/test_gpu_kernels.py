@@ -148,6 +148,22 @@ def test_gemm_skinny_bf16(m, n, k, split, wide):
     assert torch.equal(out32, K().gemm_skinny_bf16(x, w, torch.float32, n_split=split, wide=wide)), "same bits from run to run"
 
 
+@pytest.mark.parametrize("m,inter,k,split,wide", [(2, 48, 136, 0, -1), (8, 50, 1000, 2, 0), (5, 132, 4096, 4, 1),
+                                                  (8, 12288, 4096, 0, -1), (13, 39, 264, 1, 1), (8, 7, 64, 0, 0)])
+def test_gemm_skinny_swiglu_bf16(m, inter, k, split, wide):
+    """The gate/up product of decode batches with the SwiGLU in its last step: the bits of the skinny product
+    followed by the SwiGLU kernel, and close to a float32 computation of both."""
+    g = torch.Generator(device=DEV).manual_seed(m * 7 + k + inter)
+    x = torch.randn(m, k, generator=g, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(2 * inter, k, generator=g, device=DEV) * (2.0 / math.sqrt(k))).to(torch.bfloat16)
+    fused = K().gemm_skinny_swiglu_bf16(x, w, n_split=split, wide=wide)
+    two_steps = K().swiglu(K().gemm_skinny_bf16(x, w, torch.bfloat16, n_split=split, wide=wide))
+    assert fused.shape == (m, inter) and torch.equal(fused, two_steps)
+    gu = x.float() @ w.float().T
+    gate, up = gu[:, :inter].to(torch.bfloat16).float(), gu[:, inter:].to(torch.bfloat16).float()
+    torch.testing.assert_close(fused.float(), gate / (1 + torch.exp(-gate)) * up, rtol=3e-2, atol=3e-2)
+
+
 @pytest.mark.parametrize("m,n,k", [(1, 128, 64), (8, 100, 1000), (5, 264, 4096), (16, 4096, 4096), (8, 24576, 512), (3, 777, 72),
                                    (8, 4096, 12288), (2, 151936, 256), (13, 6144, 4096)])
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
