@@ -111,3 +111,62 @@ extern "C" int gi_gemv_bf16(const void* x, const void* W, void* out, int out_dty
     if (out_dtype == GI_DTYPE_F32) return launch_gemv<float>((const bf16*)x, (const bf16*)W, (float*)out, M, N, K, s);
     GI_REQUIRE(false, "gi_gemv_bf16: output dtype %d", out_dtype);
 }
+
+// One row of x against a gate and an up projection at once: W is [2 I, K] (the gate rows first), a warp takes
+// gate row n and up row I + n with eight 16-byte loads in flight per lane, and writes silu(gate) * up
+// (each factor rounded to bfloat16 as a stored product would be, then the SwiGLU kernel's arithmetic).
+__global__ void __launch_bounds__(GV_WARPS * 32)
+gemv_swiglu_bf16_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, bf16* __restrict__ out, int inter, int K) {
+    gi_pdl_launch_dependents();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n = blockIdx.x * GV_WARPS + warp;
+    if (n >= inter) return;
+    const uint4* grow = reinterpret_cast<const uint4*>(W + (size_t)n * K);
+    const uint4* urow = reinterpret_cast<const uint4*>(W + (size_t)(inter + n) * K);
+    const int nvec = K / 8;
+    float ga[1] = {0.f}, ua[1] = {0.f};
+    int v = lane;
+    // W is nobody's output: the first loads go out before the wait for the kernel that makes x
+    const bool head = v + 96 < nvec;
+    uint4 g0, g1, g2, g3, u0, u1, u2, u3;
+    if (head) {
+        g0 = ld_stream(grow + v), g1 = ld_stream(grow + v + 32), g2 = ld_stream(grow + v + 64), g3 = ld_stream(grow + v + 96);
+        u0 = ld_stream(urow + v), u1 = ld_stream(urow + v + 32), u2 = ld_stream(urow + v + 64), u3 = ld_stream(urow + v + 96);
+    }
+    gi_pdl_wait();
+    bool have = head;
+    while (true) {
+        if (have) {
+            fma8<1>(g0, x, K, v * 8, ga); fma8<1>(g1, x, K, (v + 32) * 8, ga);
+            fma8<1>(g2, x, K, (v + 64) * 8, ga); fma8<1>(g3, x, K, (v + 96) * 8, ga);
+            fma8<1>(u0, x, K, v * 8, ua); fma8<1>(u1, x, K, (v + 32) * 8, ua);
+            fma8<1>(u2, x, K, (v + 64) * 8, ua); fma8<1>(u3, x, K, (v + 96) * 8, ua);
+            v += 128;
+        }
+        have = v + 96 < nvec;
+        if (!have) break;
+        g0 = ld_stream(grow + v), g1 = ld_stream(grow + v + 32), g2 = ld_stream(grow + v + 64), g3 = ld_stream(grow + v + 96);
+        u0 = ld_stream(urow + v), u1 = ld_stream(urow + v + 32), u2 = ld_stream(urow + v + 64), u3 = ld_stream(urow + v + 96);
+    }
+    for (; v < nvec; v += 32) {
+        const uint4 gw = ld_stream(grow + v), uw = ld_stream(urow + v);
+        fma8<1>(gw, x, K, v * 8, ga);
+        fma8<1>(uw, x, K, v * 8, ua);
+    }
+    const float gate = warp_sum(ga[0]), up = warp_sum(ua[0]);
+    if (lane == 0) {
+        const float gf = __bfloat162float(__float2bfloat16_rn(gate)), uf = __bfloat162float(__float2bfloat16_rn(up));
+        out[n] = __float2bfloat16_rn(gf / (1.f + expf(-gf)) * uf);
+    }
+}
+
+// out[1, I] = silu(x . Wg^T) * (x . Wu^T) for one row x and W = [Wg; Wu] of two_inter = 2 I rows.
+extern "C" int gi_gemv_swiglu_bf16(const void* x, const void* W, void* out, int two_inter, int K, void* stream) {
+    GI_REQUIRE(two_inter > 0 && two_inter % 2 == 0 && K > 0, "gi_gemv_swiglu_bf16: W must hold a gate and an up half (%d rows)", two_inter);
+    GI_REQUIRE(K % 8 == 0, "gi_gemv_swiglu_bf16: inner size %d is no multiple of 8 (rows must start on 16 bytes)", K);
+    GI_REQUIRE(((uintptr_t)x % 16 == 0) && ((uintptr_t)W % 16 == 0), "gi_gemv_swiglu_bf16: operands must start on 16 bytes");
+    const int inter = two_inter / 2;
+    gi_launch(gemv_swiglu_bf16_kernel, dim3((inter + GV_WARPS - 1) / GV_WARPS), dim3(GV_WARPS * 32), 0, (cudaStream_t)stream,
+              (const bf16*)x, (const bf16*)W, (bf16*)out, inter, K);
+    return gi_check_launch("gi_gemv_swiglu_bf16");
+}

@@ -228,6 +228,19 @@ def gemm_skinny_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, n
     return out
 
 
+def gemv_swiglu_bf16(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
+    """silu(x . Wg^T) * (x . Wu^T) for one row x [1, K]: the bandwidth kernel with a gate and an up row per warp
+    and the activation at its end.  Returns [1, I] bfloat16, the bits of `swiglu(gemv_bf16(x, w_gate_up))`."""
+    l = require_gpu()
+    _dense(x, "x", torch.bfloat16), _dense(w_gate_up, "w_gate_up", torch.bfloat16)
+    (m, k), (n2, k2) = x.shape, w_gate_up.shape
+    if m != 1 or k != k2:
+        raise KernelError(f"gemv_swiglu_bf16 takes one row: x {tuple(x.shape)}, w {tuple(w_gate_up.shape)}")
+    out = torch.empty((1, n2 // 2), dtype=torch.bfloat16, device=x.device)
+    check(l.gi_gemv_swiglu_bf16(_ptr(x), _ptr(w_gate_up), _ptr(out), n2, k, _stream()), l)
+    return out
+
+
 def gemm_skinny_swiglu_bf16(x: torch.Tensor, w_gate_up: torch.Tensor, n_split: int = 0, wide: int = -1) -> torch.Tensor:
     """silu(x . Wg^T) * (x . Wu^T) for x [M<=16, K] and w_gate_up = [Wg; Wu] ([2 I, K], the gate first) with the
     activation in the last step of the skinny product.  Returns [M, I] bfloat16, the bits of

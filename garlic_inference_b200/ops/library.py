@@ -41,6 +41,7 @@ _SIGNATURES = {
     "gi_sgemm_nt": ([P, P, P, I, I, I, L, L, P], I),
     "gi_gemv_bf16": ([P, P, P, I, I, I, I, P], I),
     "gi_gemm_skinny_bf16": ([P, P, P, I, I, I, I, I, I, P], I),
+    "gi_gemv_swiglu_bf16": ([P, P, P, I, I, P], I),
     "gi_gemm_skinny_swiglu_bf16": ([P, P, P, I, I, I, I, I, P], I),
     "gi_gemm_tcgen05_swiglu_bf16": ([P, P, P, I, I, I, P, P], I),
     "gi_gemm_streamk_bf16": ([P, P, P, I, I, I, I, P, P, P, P], I),

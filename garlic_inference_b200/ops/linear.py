@@ -79,15 +79,16 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
 
 def swiglu_product(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
     """silu(x . Wg^T) * (x . Wu^T) for the packed weight [Wg; Wu]: prompts in bfloat16 run it as one tcgen05
-    kernel (product and activation), decode batches of 2 to 8 as one skinny kernel, everything else as the
+    kernel (product and activation), decode batches of 1 to 8 as one gemv or skinny kernel, everything else as the
     product of `linear` and the SwiGLU kernel.  Same bits every way for the same product kernel."""
     m, k = x.shape
     if (FUSED_SWIGLU_MIN_ROWS > 0 and m >= FUSED_SWIGLU_MIN_ROWS and x.dtype == torch.bfloat16
             and w_gate_up.dtype == torch.bfloat16 and k % 8 == 0 and w_gate_up.shape[0] % 2 == 0
             and x.data_ptr() % 16 == 0 and w_gate_up.data_ptr() % 16 == 0):
         return kernels.gemm_tcgen05_swiglu_bf16(x, w_gate_up)
-    if (GEMV_MAX_ROWS < m <= SKINNY_MAX_ROWS and x.dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16
+    if (0 < m <= SKINNY_MAX_ROWS and x.dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16
             and k % 8 == 0 and w_gate_up.shape[0] % 2 == 0 and x.data_ptr() % 16 == 0 and w_gate_up.data_ptr() % 16 == 0
             and not (0 < STREAMK_MIN_BYTES <= w_gate_up.numel() * 2)):
-        return kernels.gemm_skinny_swiglu_bf16(x, w_gate_up)      # decode batches: the activation in the product's last step
+        # decode batches: the activation in the product's last step
+        return kernels.gemv_swiglu_bf16(x, w_gate_up) if m <= GEMV_MAX_ROWS else kernels.gemm_skinny_swiglu_bf16(x, w_gate_up)
     return kernels.swiglu(linear(x, w_gate_up))

@@ -148,6 +148,19 @@ def test_gemm_skinny_bf16(m, n, k, split, wide):
     assert torch.equal(out32, K().gemm_skinny_bf16(x, w, torch.float32, n_split=split, wide=wide)), "same bits from run to run"
 
 
+@pytest.mark.parametrize("inter,k", [(48, 136), (50, 1000), (12288, 4096), (7, 64), (1001, 1288)])
+def test_gemv_swiglu_bf16(inter, k):
+    g = torch.Generator(device=DEV).manual_seed(k + inter)
+    x = torch.randn(1, k, generator=g, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(2 * inter, k, generator=g, device=DEV) * (2.0 / math.sqrt(k))).to(torch.bfloat16)
+    fused = K().gemv_swiglu_bf16(x, w)
+    two_steps = K().swiglu(K().gemv_bf16(x, w, torch.bfloat16))
+    assert fused.shape == (1, inter) and torch.equal(fused, two_steps)
+    gu = x.float() @ w.float().T
+    gate, up = gu[:, :inter].to(torch.bfloat16).float(), gu[:, inter:].to(torch.bfloat16).float()
+    torch.testing.assert_close(fused.float(), gate / (1 + torch.exp(-gate)) * up, rtol=3e-2, atol=3e-2)
+
+
 @pytest.mark.parametrize("m,inter,k,split,wide", [(2, 48, 136, 0, -1), (8, 50, 1000, 2, 0), (5, 132, 4096, 4, 1),
                                                   (8, 12288, 4096, 0, -1), (13, 39, 264, 1, 1), (8, 7, 64, 0, 0)])
 def test_gemm_skinny_swiglu_bf16(m, inter, k, split, wide):
