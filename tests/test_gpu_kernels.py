@@ -633,6 +633,38 @@ def test_attention_decode_tcgen05_finds_one_far_key():
     assert int(K().tcgen05_error_flag(q.device).item()) == 0
 
 
+@pytest.mark.parametrize("kernel", ["decode", "prefill"])
+def test_tcgen05_attention_over_thousands_of_keys(kernel):
+    """4,100 cached keys (65 tiles, 16 slices in the decode kernel): one far key that carries all the weight is
+    found wherever it lies, and with ordinary scores the result agrees with the plain softmax."""
+    n_q, n_kv, d, page, n = 8, 2, 128, 64, 4100
+    pos = torch.tensor([n - 1], dtype=torch.int32, device=DEV)
+    slot = torch.zeros(1, dtype=torch.int32, device=DEV)
+    tiles = _tiles128_for([(0, 0, 1, n - 1)])
+
+    def attend(q, k_pool, v_pool, bt, window=0):
+        if kernel == "decode":
+            return K().attention_decode_tcgen05(q, k_pool, v_pool, bt, pos, slot, 1.0, window).float().view(n_q, d)
+        return K().attention_prefill_tcgen05(q, k_pool, v_pool, bt, tiles, 1.0, window).float().view(n_q, d)
+
+    for far in (0, 2047, 2048, 4099):
+        k_pool, v_pool, bt, kd, vd = make_cache(1, [n], n_kv, d, page, torch.bfloat16, seed=far + 9)
+        q = torch.zeros(1, n_q, d, device=DEV)
+        for h in range(n_q):
+            q[0, h] = kd[0][far, h // 4] * 2.0
+        out = attend(q.to(torch.bfloat16), k_pool, v_pool, bt)
+        for h in range(n_q):
+            torch.testing.assert_close(out[h], vd[0][far, h // 4], rtol=2e-2, atol=2e-2,
+                                       msg=lambda msg: f"{kernel}: far key {far}, head {h}: {msg}")
+    g = torch.Generator(device=DEV).manual_seed(3)
+    q = (torch.randn(1, n_q, d, generator=g, device=DEV) * 0.3).to(torch.bfloat16)
+    for window in (0, 1000):
+        out = attend(q, k_pool, v_pool, bt, window)
+        ref = ref_attention(q[0].float(), kd[0], vd[0], n - 1, 1.0, window).float()
+        torch.testing.assert_close(out, ref, rtol=2e-2, atol=2e-2)
+    assert int(K().tcgen05_error_flag(q.device).item()) == 0
+
+
 def _tiles128_for(runs):
     out = []
     for slot, row0, n, pos0 in runs:
