@@ -324,3 +324,126 @@ def test_layer_order_is_data(dtype, tmp_path):
         got = tiny.run_trace_in_process(model, steps)
         tiny.assert_covers(got, reqs)
         tiny.compare(got, want, tiny.TOL[dtype], f"looped {dtype}")
+
+
+# ---------------------------------------------------------------------------------------------------
+# generality: a toy feed-forward with routing and a toy position encoding, registered from outside
+# ---------------------------------------------------------------------------------------------------
+def _toy_routed_classes():
+    """A feed-forward that sends every token to one of three small experts (the router's largest logit, ties to
+    the lowest index, router in float32), and learned absolute positions added to the embedded tokens in place
+    of rotations.  Both live in this test; the framework's files do not know them."""
+    import dataclasses
+    from garlic_inference_b200 import Qwen3Config, register_architecture, register_part
+    from garlic_inference_b200.config.base import PartSpec
+    from garlic_inference_b200.parts import FeedForward, PositionEncoding
+    from garlic_inference_b200.weights import TensorWant
+
+    class Top1Experts(FeedForward):
+        kind = "toy_top1_experts"
+
+        @classmethod
+        def wanted(cls, params):
+            h, e, w = params["hidden_size"], params["n_experts"], params["expert_width"]
+            return {"router": TensorWant((e, h)), "w_in": TensorWant((e * w, h)), "w_out": TensorWant((e * h, w))}
+
+        def __init__(self, params, load, rt):
+            super().__init__(params, load, rt)
+            self.h, self.e, self.w = params["hidden_size"], params["n_experts"], params["expert_width"]
+            self.router = load("router").float()
+            self.w_in = load("w_in").float().view(self.e, self.w, self.h)
+            self.w_out = load("w_out").float().view(self.e, self.h, self.w)
+
+        def step(self, x, ctx):
+            xf = x.float()
+            choice = (xf @ self.router.T).argmax(dim=-1)          # first maximum = lowest index
+            out = torch.zeros_like(xf)
+            for e in range(self.e):                               # tokens gathered per expert, results scattered back
+                rows = (choice == e).nonzero().flatten()
+                if rows.numel():
+                    hid = torch.relu(xf[rows] @ self.w_in[e].T)
+                    out[rows] = hid @ self.w_out[e].T
+            return out.to(x.dtype)
+
+    class LearnedPositions(PositionEncoding):
+        kind = "toy_learned_positions"
+
+        @classmethod
+        def wanted(cls, params):
+            return {"table": TensorWant((params["max_positions"], params["hidden_size"]))}
+
+        def __init__(self, params, load, rt):
+            super().__init__(params, load, rt)
+            self.table = load("table").float()
+
+        def on_embedding(self, residual, ctx):
+            residual += self.table[ctx.tok_pos.long()]            # padding rows get position 0: they are nobody's rows
+
+    class RoutedConfig(Qwen3Config):
+        def plan(self):
+            base = super().plan()
+            layers = []
+            for i, layer in enumerate(base.layers):
+                ff = PartSpec("toy_top1_experts", dict(hidden_size=self.hidden_size, n_experts=3, expert_width=40),
+                              {k: f"model.layers.{i}.experts.{k}" for k in ("router", "w_in", "w_out")})
+                layers.append(dataclasses.replace(layer, feed_forward=ff if i % 2 == 0 else layer.feed_forward,
+                                                  position="learned"))
+            positions = {"learned": PartSpec("toy_learned_positions",
+                                             dict(max_positions=self.max_position_embeddings, hidden_size=self.hidden_size),
+                                             dict(table="model.positions.weight"))}
+            return dataclasses.replace(base, architecture="ToyRoutedForCausalLM", layers=tuple(layers), positions=positions)
+
+    register_part("toy_top1_experts", Top1Experts)
+    register_part("toy_learned_positions", LearnedPositions)
+    register_architecture("ToyRoutedForCausalLM", RoutedConfig)
+    return RoutedConfig
+
+
+def _plain_routed_forward(cfg, w, ids):
+    """The same model, plainly: learned positions on the embedding, attention without rotation, experts on the
+    even layers."""
+    ids = torch.as_tensor(ids)
+    n = len(ids)
+    h = plain.embed(ids, w["model.embed_tokens.weight"]) + w["model.positions.weight"][:n].float()
+    d, n_q, n_kv = cfg["head_dim"], cfg["num_attention_heads"], cfg["num_key_value_heads"]
+    for i in range(cfg["num_hidden_layers"]):
+        p = f"model.layers.{i}."
+        x = plain.rms_norm(h, w[p + "input_layernorm.weight"], cfg["rms_norm_eps"])
+        q = (x @ w[p + "self_attn.q_proj.weight"].float().T).view(n, n_q, d)
+        k = (x @ w[p + "self_attn.k_proj.weight"].float().T).view(n, n_kv, d)
+        v = (x @ w[p + "self_attn.v_proj.weight"].float().T).view(n, n_kv, d)
+        q = plain.rms_norm(q, w[p + "self_attn.q_norm.weight"], cfg["rms_norm_eps"])
+        k = plain.rms_norm(k, w[p + "self_attn.k_norm.weight"], cfg["rms_norm_eps"])
+        o = plain.attention_scores(q, k, v, None)
+        r = o.reshape(n, n_q * d) @ w[p + "self_attn.o_proj.weight"].float().T + h
+        x = plain.rms_norm(r, w[p + "post_attention_layernorm.weight"], cfg["rms_norm_eps"])
+        if i % 2 == 0:
+            router = w[p + "experts.router"].float()
+            w_in = w[p + "experts.w_in"].float().view(3, 40, -1)
+            w_out = w[p + "experts.w_out"].float().view(3, -1, 40)
+            choice = (x @ router.T).argmax(dim=-1)
+            m = torch.stack([torch.relu(x[t] @ w_in[c].T) @ w_out[c].T for t, c in enumerate(choice.tolist())])
+        else:
+            m = plain.swiglu_mlp(x, w, p + "mlp.")
+        h = m + r
+    return plain.output_head(h, w, cfg)
+
+
+def test_a_toy_routed_feed_forward_and_learned_positions_are_registered_built_and_stepped(tmp_path):
+    from garlic_inference_b200 import AutoModel, write_random_model
+    RoutedConfig = _toy_routed_classes()
+    cfg_obj = RoutedConfig(**{**tiny.TINY["A"]["cfg"], "num_hidden_layers": 3, "max_position_embeddings": 96,
+                              "architectures": ["ToyRoutedForCausalLM"]})
+    d = write_random_model(tmp_path / "routed", cfg_obj, seed=8, std=0.08, norm_std=0.1)
+    model = AutoModel.from_pretrained(d, device=0, dtype="float32", max_tokens=512, page_size=16)
+    assert type(model.config) is RoutedConfig
+    cfg, w = plain.read_model_dir(d)
+    assert "model.layers.0.experts.router" in w and "model.layers.1.experts.router" not in w
+    assert "model.layers.0.mlp.gate_proj.weight" not in w, "a layer's feed-forward weights are those of its own part"
+    reqs = tiny.random_requests(512, [30, 7, 64, 21], seed=31)
+    want = {rid: _plain_routed_forward(cfg, w, t).numpy() for rid, t in reqs.items()}
+    for steps in (tiny.trace_whole(reqs), tiny.trace_tail_by_one(reqs, tail=16),
+                  tiny.trace_batched(reqs, [["r0", "r1"], ["r2", "r3"]])):
+        got = tiny.run_trace_in_process(model, steps)
+        tiny.assert_covers(got, reqs)
+        tiny.compare(got, want, tiny.TOL["float32"], "toy routed float32")
