@@ -143,21 +143,32 @@ gemm_streamk_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __g
     const long long u0 = units * c / G, u1 = units * (c + 1) / G;
     volatile int* abort = &ctl->abort;
 
+    // The start is kept short: the lane that issues the copies sets up the barriers itself and goes straight to
+    // its copies (their descriptors asked for first of all); the other warps meet it at a named barrier only to
+    // see the barriers initialised and, among themselves, the tensor memory allocated.
     if (threadIdx.x == 0) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
         for (int s = 0; s < SKT_STAGES; ++s) { skt_mbar_init(&ctl->full[s], 1); skt_mbar_init(&ctl->empty[s], 1); }
         for (int b = 0; b < 2; ++b) { skt_mbar_init(&ctl->acc_full[b], 1); skt_mbar_init(&ctl->acc_empty[b], 4); }
         ctl->abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                     ::"r"(skt_smem(&ctl->tmem_base)), "r"(SKT_TMEM_COLS) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    uint32_t tmem = 0;
+    if (warp == 0) {
+        __syncwarp();
+        asm volatile("bar.arrive 2, 192;" ::: "memory");             // the barriers are set up; does not wait
+    } else {
+        if (warp == 1) {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                         ::"r"(skt_smem(&ctl->tmem_base)), "r"(SKT_TMEM_COLS) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        asm volatile("bar.sync 2, 192;" ::: "memory");
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        tmem = ctl->tmem_base;
     }
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const uint32_t tmem = ctl->tmem_base;
 
     if (warp == 0) {
         if (lane == 0) {
