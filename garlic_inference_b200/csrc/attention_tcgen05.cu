@@ -1,22 +1,23 @@
 // bfloat16 flash attention for prompts on the fifth-generation tensor cores: head_dim 128, cache pages
 // that are a multiple of 64 tokens.
 //
-// One CTA takes 128 consecutive queries of one sequence and one query head, and walks the keys of the
-// sequence's cache 64 at a time; two CTAs share an SM, so that one's softmax runs under the other's products:
-//   warp 0, one lane:  TMA.  The query tile once; per key tile the 64 keys and 64 values of the tile's
+// A work item is 128 consecutive queries of one sequence and one query head; its CTA walks the keys of the
+// sequence's cache 64 at a time.  The grid is persistent, two CTAs to an SM (one's softmax runs under the
+// other's products), and every CTA takes several items, a long one with a short one (see the kernel):
+//   warp 0, one lane:  TMA.  The item's query tile; per key tile the 64 keys and 64 values of the tile's
 //                      page (the pools are 2-D tensor maps [all rows, head_dim]; a tile never crosses a
 //                      page), into rings of two stages each for keys and for values, 128-byte swizzled.
 //   warp 1, one lane:  MMA.  S = Q K^T (128 x 64, float32) into one of two buffers in tensor memory, one
 //                      tile ahead of the softmax; when the softmax warps have written the probabilities
 //                      over the scores as bfloat16, O += P V (128 x 128) with P read from tensor memory
-//                      and V from shared memory.  O stays in tensor memory for all tiles.
+//                      and V from shared memory.  O stays in tensor memory for all tiles of an item.
 //   warps 2..5:        softmax.  Thread i owns query row i: it reads its row of S from tensor memory,
 //                      scales and masks it (causal, window), and writes exp2(s - ref).  `ref` follows
 //                      the row's running maximum lazily: only when the maximum has grown by more than
 //                      FT_LAZY (in powers of two) are ref, the running sum and the row of O in tensor
 //                      memory rescaled; until then probabilities up to 2^FT_LAZY are simply accumulated,
 //                      which float32 holds exactly as well.  No shuffles, no shared memory, and O is
-//                      read once, at the end.
+//                      read once, at the end of the item.  The barriers' phases run on from item to item.
 //
 // Scores, softmax and the output sum are float32; probabilities are rounded to bfloat16 for the second
 // product.  Every wait on an mbarrier is bounded: when one runs out, a code goes to *error_flag, all
