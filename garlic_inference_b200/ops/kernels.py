@@ -361,7 +361,7 @@ def mma_attention_takes(dtype: torch.dtype, head_dim: int) -> bool:
 
 
 def attention_prefill_bf16(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: torch.Tensor,
-                           q_tiles: torch.Tensor, scale: float, window: int) -> torch.Tensor:
+                           q_tiles: torch.Tensor, scale: float, window: int, rows_covered: bool = False) -> torch.Tensor:
     """Flash attention of q [n, n_q, d] over the paged cache for steps with several tokens per sequence.
     `q_tiles` int32 [n_tiles, 4] cuts the rows into runs of at most 64 consecutive tokens of one
     sequence: {slot, first row, rows, position of the first row}.  Returns [n, n_q * d]."""
@@ -374,7 +374,8 @@ def attention_prefill_bf16(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.
         raise KernelError(f"cache pools {tuple(k_pool.shape)} do not fit head_dim {d}")
     if q_tiles.dim() != 2 or q_tiles.shape[1] != 4 or q_tiles.data_ptr() % 16:
         raise KernelError("q_tiles must be int32 [n_tiles, 4] starting on 16 bytes")
-    out = torch.zeros((n, n_q * d), dtype=q.dtype, device=q.device)       # rows in no tile (padding) stay zero
+    # rows in no tile (padding) stay zero; when the caller says that every row lies in a tile, nothing is filled
+    out = (torch.empty if rows_covered else torch.zeros)((n, n_q * d), dtype=q.dtype, device=q.device)
     check(l.gi_attention_prefill_bf16(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_table), _ptr(q_tiles),
                                       q_tiles.shape[0], _ptr(out), n_q, n_kv, d, page_size, block_table.shape[1],
                                       n_pages, int(window or 0), float(scale), _stream()), l)
@@ -387,7 +388,7 @@ def tcgen05_attention_takes(dtype: torch.dtype, head_dim: int, page_size: int) -
 
 
 def attention_prefill_tcgen05(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: torch.Tensor,
-                              q_tiles128: torch.Tensor, scale: float, window: int) -> torch.Tensor:
+                              q_tiles128: torch.Tensor, scale: float, window: int, rows_covered: bool = False) -> torch.Tensor:
     """Flash attention of q [n, n_q, 128] over the paged cache on tcgen05 tensor cores (TMA-fed, S, P and
     P V in tensor memory).  `q_tiles128` int32 [n_tiles, 4] cuts the rows into runs of at most 128
     consecutive tokens of one sequence: {slot, first row, rows, position of the first row}."""
@@ -400,7 +401,8 @@ def attention_prefill_tcgen05(q: torch.Tensor, k_pool: torch.Tensor, v_pool: tor
         raise KernelError(f"cache pools {tuple(k_pool.shape)} do not fit head_dim {d}")
     if q_tiles128.dim() != 2 or q_tiles128.shape[1] != 4 or q_tiles128.data_ptr() % 16:
         raise KernelError("q_tiles128 must be int32 [n_tiles, 4] starting on 16 bytes")
-    out = torch.zeros((n, n_q * d), dtype=q.dtype, device=q.device)       # rows in no tile (padding) stay zero
+    # rows in no tile (padding) stay zero; when the caller says that every row lies in a tile, nothing is filled
+    out = (torch.empty if rows_covered else torch.zeros)((n, n_q * d), dtype=q.dtype, device=q.device)
     check(l.gi_attention_prefill_tcgen05(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_table), _ptr(q_tiles128),
                                          q_tiles128.shape[0], _ptr(out), n, n_q, n_kv, d, page_size,
                                          block_table.shape[1], n_pages, int(window or 0), float(scale),

@@ -86,7 +86,8 @@ class GQAAttention(Mixer):
         if (not ctx.all_single and ctx.q_tiles128 is not None
                 and kernels.tcgen05_attention_takes(q.dtype, self.d, kv.page_size)):
             return kernels.attention_prefill_tcgen05(q, kv.k_pool, kv.v_pool, kv.block_table, ctx.q_tiles128,
-                                                     self.scale, self.window or 0)
+                                                     self.scale, self.window or 0,
+                                                     rows_covered=ctx.n_tokens == sum(ctx.seq_lens))
         if ctx.all_single and kernels.tcgen05_decode_takes(q.dtype, self.d, kv.page_size, self.n_q // self.n_kv):
             return kernels.attention_decode_tcgen05(q, kv.k_pool, kv.v_pool, kv.block_table, ctx.tok_pos, ctx.tok_slot,
                                                     self.scale, self.window or 0)
@@ -96,7 +97,8 @@ class GQAAttention(Mixer):
                                                      ctx.tok_slot, self.scale, self.window or 0)
             if not ctx.all_single and ctx.q_tiles is not None:
                 return kernels.attention_prefill_bf16(q, kv.k_pool, kv.v_pool, kv.block_table, ctx.q_tiles,
-                                                      self.scale, self.window or 0)
+                                                      self.scale, self.window or 0,
+                                                      rows_covered=ctx.n_tokens == sum(ctx.seq_lens))
         return kernels.attention_generic(q, kv.k_pool, kv.v_pool, kv.block_table, ctx.tok_pos, ctx.tok_slot,
                                          self.scale, self.window or 0, ctx.status)
 
