@@ -47,31 +47,33 @@ gemv_bf16_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, OutT* _
     float acc[M];
 #pragma unroll
     for (int m = 0; m < M; ++m) acc[m] = 0.f;
-    int v = lane;
+    // The row is walked in groups of 128 vectors (four loads per lane), from a group that differs from row to
+    // row, wrapping around: warps that all begin at the start of their rows ask the same few memory channels at
+    // the same time.  The order of a row's sum is fixed by the row's number.
+    const int groups = nvec / 128;
+    const int g0 = groups > 0 ? (int)(((unsigned)n * 13u) % (unsigned)groups) : 0;
+    int v = g0 * 128 + lane;
     // W is nobody's output: the first loads go out before the wait for the kernel that makes x
-    const bool head = v + 96 < nvec;
     uint4 h0, h1, h2, h3;
-    if (head) {
+    if (groups > 0) {
         h0 = ld_stream(wrow + v), h1 = ld_stream(wrow + v + 32);
         h2 = ld_stream(wrow + v + 64), h3 = ld_stream(wrow + v + 96);
     }
     gi_pdl_wait();
-    if (head) {
-        fma8<M>(h0, x, K, v * 8, acc);
-        fma8<M>(h1, x, K, (v + 32) * 8, acc);
-        fma8<M>(h2, x, K, (v + 64) * 8, acc);
-        fma8<M>(h3, x, K, (v + 96) * 8, acc);
-        v += 128;
+    for (int j = 0; j < groups; ++j) {
+        const int cur = v;
+        const uint4 w0 = h0, w1 = h1, w2 = h2, w3 = h3;
+        if (j + 1 < groups) {                    // the next group's loads go out before this one is multiplied
+            v = (g0 + j + 1 < groups ? g0 + j + 1 : g0 + j + 1 - groups) * 128 + lane;
+            h0 = ld_stream(wrow + v), h1 = ld_stream(wrow + v + 32);
+            h2 = ld_stream(wrow + v + 64), h3 = ld_stream(wrow + v + 96);
+        }
+        fma8<M>(w0, x, K, cur * 8, acc);
+        fma8<M>(w1, x, K, (cur + 32) * 8, acc);
+        fma8<M>(w2, x, K, (cur + 64) * 8, acc);
+        fma8<M>(w3, x, K, (cur + 96) * 8, acc);
     }
-    for (; v + 96 < nvec; v += 128) {
-        const uint4 w0 = ld_stream(wrow + v), w1 = ld_stream(wrow + v + 32);
-        const uint4 w2 = ld_stream(wrow + v + 64), w3 = ld_stream(wrow + v + 96);
-        fma8<M>(w0, x, K, v * 8, acc);
-        fma8<M>(w1, x, K, (v + 32) * 8, acc);
-        fma8<M>(w2, x, K, (v + 64) * 8, acc);
-        fma8<M>(w3, x, K, (v + 96) * 8, acc);
-    }
-    for (; v < nvec; v += 32) {
+    for (v = groups * 128 + lane; v < nvec; v += 32) {
         const uint4 w0 = ld_stream(wrow + v);
         fma8<M>(w0, x, K, v * 8, acc);
     }
@@ -125,30 +127,33 @@ gemv_swiglu_bf16_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, 
     const uint4* urow = reinterpret_cast<const uint4*>(W + (size_t)(inter + n) * K);
     const int nvec = K / 8;
     float ga[1] = {0.f}, ua[1] = {0.f};
-    int v = lane;
-    // W is nobody's output: the first loads go out before the wait for the kernel that makes x
-    const bool head = v + 96 < nvec;
+    // each row from the group its own number gives it, as in the kernel above (the same sums, bit for bit)
+    const int groups = nvec / 128;
+    const int gs = groups > 0 ? (int)(((unsigned)n * 13u) % (unsigned)groups) : 0;
+    const int us = groups > 0 ? (int)(((unsigned)(inter + n) * 13u) % (unsigned)groups) : 0;
+    int gv = gs * 128 + lane, uv = us * 128 + lane;
     uint4 g0, g1, g2, g3, u0, u1, u2, u3;
-    if (head) {
-        g0 = ld_stream(grow + v), g1 = ld_stream(grow + v + 32), g2 = ld_stream(grow + v + 64), g3 = ld_stream(grow + v + 96);
-        u0 = ld_stream(urow + v), u1 = ld_stream(urow + v + 32), u2 = ld_stream(urow + v + 64), u3 = ld_stream(urow + v + 96);
+    // W is nobody's output: the first loads go out before the wait for the kernel that makes x
+    if (groups > 0) {
+        g0 = ld_stream(grow + gv), g1 = ld_stream(grow + gv + 32), g2 = ld_stream(grow + gv + 64), g3 = ld_stream(grow + gv + 96);
+        u0 = ld_stream(urow + uv), u1 = ld_stream(urow + uv + 32), u2 = ld_stream(urow + uv + 64), u3 = ld_stream(urow + uv + 96);
     }
     gi_pdl_wait();
-    bool have = head;
-    while (true) {
-        if (have) {
-            fma8<1>(g0, x, K, v * 8, ga); fma8<1>(g1, x, K, (v + 32) * 8, ga);
-            fma8<1>(g2, x, K, (v + 64) * 8, ga); fma8<1>(g3, x, K, (v + 96) * 8, ga);
-            fma8<1>(u0, x, K, v * 8, ua); fma8<1>(u1, x, K, (v + 32) * 8, ua);
-            fma8<1>(u2, x, K, (v + 64) * 8, ua); fma8<1>(u3, x, K, (v + 96) * 8, ua);
-            v += 128;
+    for (int j = 0; j < groups; ++j) {
+        const int gc = gv, uc = uv;
+        const uint4 a0 = g0, a1 = g1, a2 = g2, a3 = g3, b0 = u0, b1 = u1, b2 = u2, b3 = u3;
+        if (j + 1 < groups) {
+            gv = (gs + j + 1 < groups ? gs + j + 1 : gs + j + 1 - groups) * 128 + lane;
+            uv = (us + j + 1 < groups ? us + j + 1 : us + j + 1 - groups) * 128 + lane;
+            g0 = ld_stream(grow + gv), g1 = ld_stream(grow + gv + 32), g2 = ld_stream(grow + gv + 64), g3 = ld_stream(grow + gv + 96);
+            u0 = ld_stream(urow + uv), u1 = ld_stream(urow + uv + 32), u2 = ld_stream(urow + uv + 64), u3 = ld_stream(urow + uv + 96);
         }
-        have = v + 96 < nvec;
-        if (!have) break;
-        g0 = ld_stream(grow + v), g1 = ld_stream(grow + v + 32), g2 = ld_stream(grow + v + 64), g3 = ld_stream(grow + v + 96);
-        u0 = ld_stream(urow + v), u1 = ld_stream(urow + v + 32), u2 = ld_stream(urow + v + 64), u3 = ld_stream(urow + v + 96);
+        fma8<1>(a0, x, K, gc * 8, ga); fma8<1>(a1, x, K, (gc + 32) * 8, ga);
+        fma8<1>(a2, x, K, (gc + 64) * 8, ga); fma8<1>(a3, x, K, (gc + 96) * 8, ga);
+        fma8<1>(b0, x, K, uc * 8, ua); fma8<1>(b1, x, K, (uc + 32) * 8, ua);
+        fma8<1>(b2, x, K, (uc + 64) * 8, ua); fma8<1>(b3, x, K, (uc + 96) * 8, ua);
     }
-    for (; v < nvec; v += 32) {
+    for (int v = groups * 128 + lane; v < nvec; v += 32) {
         const uint4 gw = ld_stream(grow + v), uw = ld_stream(urow + v);
         fma8<1>(gw, x, K, v * 8, ga);
         fma8<1>(uw, x, K, v * 8, ua);

@@ -243,8 +243,8 @@ def gemv_swiglu_bf16(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
 
 def gemm_skinny_swiglu_bf16(x: torch.Tensor, w_gate_up: torch.Tensor, n_split: int = 0, wide: int = -1) -> torch.Tensor:
     """silu(x . Wg^T) * (x . Wu^T) for x [M<=16, K] and w_gate_up = [Wg; Wu] ([2 I, K], the gate first) with the
-    activation in the last step of the skinny product.  Returns [M, I] bfloat16, the bits of
-    `swiglu(gemm_skinny_bf16(x, w_gate_up))`."""
+    activation in the last step of the skinny product.  Returns [M, I] bfloat16: `swiglu(gemm_skinny_bf16(x,
+    w_gate_up))` up to the rounding of the sums (the kernels walk K in different orders)."""
     l = require_gpu()
     _dense(x, "x", torch.bfloat16), _dense(w_gate_up, "w_gate_up", torch.bfloat16)
     (m, k), (n2, k2) = x.shape, w_gate_up.shape

@@ -80,7 +80,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
 def swiglu_product(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
     """silu(x . Wg^T) * (x . Wu^T) for the packed weight [Wg; Wu]: prompts in bfloat16 run it as one tcgen05
     kernel (product and activation), decode batches of 1 to 8 as one gemv or skinny kernel, everything else as the
-    product of `linear` and the SwiGLU kernel.  Same bits every way for the same product kernel."""
+    product of `linear` and the SwiGLU kernel."""
     m, k = x.shape
     if (FUSED_SWIGLU_MIN_ROWS > 0 and m >= FUSED_SWIGLU_MIN_ROWS and x.dtype == torch.bfloat16
             and w_gate_up.dtype == torch.bfloat16 and k % 8 == 0 and w_gate_up.shape[0] % 2 == 0
