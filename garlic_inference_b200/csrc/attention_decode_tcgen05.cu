@@ -197,6 +197,40 @@ decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = ctl->tmem_base;
+
+    // the lane that issues the copies
+    const int* bt_row = block_table + (size_t)slot * max_pages;
+    auto tile_row = [&](int it) {
+        const int key0 = (kt_lo + t0 + it) * FD_BN;
+        const int lp = key0 / page_size;
+        int page = lp < max_pages ? bt_row[lp] : -1;
+        if (page < 0 || page >= n_pool_pages) { atomicExch(error_flag, FD_ERR_PAGE); page = 0; }
+        return (page * n_kv + kvh) * page_size + (key0 - lp * page_size);
+    };
+    int armed_k = 0, armed_v = 0;
+    auto load = [&](int it, bool keys) -> bool {
+        const int s = it % FD_STAGES;
+        unsigned long long* empty = keys ? &ctl->k_empty[s] : &ctl->v_empty[s];
+        unsigned long long* full = keys ? &ctl->k_full[s] : &ctl->v_full[s];
+        if (!fd_mbar_wait(empty, ((it / FD_STAGES) & 1) ^ 1, abort)) return false;
+        const int row = tile_row(it);
+        unsigned char* dst = (keys ? k_tiles : v_tiles) + s * FD_KV_BYTES;
+        fd_mbar_expect_tx(full, FD_KV_BYTES);
+        fd_tma_load_2d(dst, keys ? &map_k : &map_v, 0, row, full);
+        fd_tma_load_2d(dst + FD_KV_BYTES / 2, keys ? &map_k : &map_v, 64, row, full);
+        (keys ? armed_k : armed_v) = it + 1;
+        return true;
+    };
+    int next_k = 0, next_v = 0;
+    bool copies_ok = true;
+    if (warp == 0 && lane == 0) {
+        // Tiles that end before this step's token hold keys and values of earlier steps only, and the block
+        // table is set before the step's first kernel: the first ring of them goes out before the wait (their
+        // stages are free, so nothing here waits for a product that needs q).
+        auto settled = [&](int it) { return (kt_lo + t0 + it + 1) * FD_BN <= pos; };
+        while (copies_ok && next_k < min(n_tiles, FD_STAGES) && settled(next_k)) copies_ok = load(next_k++, true);
+        while (copies_ok && next_v < min(n_tiles, FD_STAGES) && settled(next_v)) copies_ok = load(next_v++, false);
+    }
     gi_pdl_wait();                               // q and the newest key come from the kernel before this one
 
     if (warp == 0) {
@@ -204,32 +238,10 @@ decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             fd_mbar_expect_tx(&ctl->q_full, FD_Q_BYTES);
             fd_tma_load_2d(q_tile, &map_q, 0, (int)row_base, &ctl->q_full);
             fd_tma_load_2d(q_tile + FD_Q_HALF, &map_q, 64, (int)row_base, &ctl->q_full);
-            const int* bt_row = block_table + (size_t)slot * max_pages;
-            auto tile_row = [&](int it) {
-                const int key0 = (kt_lo + t0 + it) * FD_BN;
-                const int lp = key0 / page_size;
-                int page = lp < max_pages ? bt_row[lp] : -1;
-                if (page < 0 || page >= n_pool_pages) { atomicExch(error_flag, FD_ERR_PAGE); page = 0; }
-                return (page * n_kv + kvh) * page_size + (key0 - lp * page_size);
-            };
-            int armed_k = 0, armed_v = 0;
-            auto load = [&](int it, bool keys) -> bool {
-                const int s = it % FD_STAGES;
-                unsigned long long* empty = keys ? &ctl->k_empty[s] : &ctl->v_empty[s];
-                unsigned long long* full = keys ? &ctl->k_full[s] : &ctl->v_full[s];
-                if (!fd_mbar_wait(empty, ((it / FD_STAGES) & 1) ^ 1, abort)) return false;
-                const int row = tile_row(it);
-                unsigned char* dst = (keys ? k_tiles : v_tiles) + s * FD_KV_BYTES;
-                fd_mbar_expect_tx(full, FD_KV_BYTES);
-                fd_tma_load_2d(dst, keys ? &map_k : &map_v, 0, row, full);
-                fd_tma_load_2d(dst + FD_KV_BYTES / 2, keys ? &map_k : &map_v, 64, row, full);
-                (keys ? armed_k : armed_v) = it + 1;
-                return true;
-            };
-            bool ok = load(0, true);
-            for (int it = 0; it < n_tiles && ok; ++it) {
-                if (it + 1 < n_tiles) ok = load(it + 1, true);
-                if (ok) ok = load(it, false);
+            bool ok = copies_ok;
+            for (int it = 0; it < n_tiles && ok; ++it) {         // keys one tile ahead of the values
+                while (ok && next_k < n_tiles && next_k <= it + 1) ok = load(next_k++, true);
+                while (ok && next_v <= it) ok = load(next_v++, false);
             }
             if (!ok && !*abort) { *abort = 1; atomicExch(error_flag, FD_ERR_PRODUCER); }
             if (*abort) {                                // no copy may be in flight when the CTA leaves
