@@ -41,10 +41,10 @@ typedef __nv_bfloat16 bf16;
 // launches carry the attribute below, it lets the next kernel of the stream be launched while this one
 // still runs (its blocks then sit in their own gi_pdl_start until this grid has finished and its writes
 // are visible).  Nothing may be read or written before it.  Without the attribute both instructions do
-// nothing.  Measured on a B200 inside the recorded decode step of Qwen3-8B sizes, with the products
-// fetching their first weights before the wait: batch 8 +1 to 4 %, batch 64 +1 %, batch 1 -2 %.  So the
-// engine asks for it (gi_set_pdl) while it records steps of two and more sequences, and nowhere else;
-// GARLIC_B200_PDL=0 or =1 in the environment overrides that for the whole process.
+// nothing.  Measured on a B200 inside the recorded decode step of Qwen3-8B sizes, with the kernels
+// requesting before the wait what no kernel of the step writes (weights, tables, the cache of earlier
+// steps): batch 8 +7 %, batch 1 +11 %, batch 64 +1 %.  The engine asks for it (gi_set_pdl) while it records
+// decode steps, and nowhere else; GARLIC_B200_PDL=0 or =1 in the environment overrides that for the process.
 __device__ __forceinline__ void gi_pdl_start() {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");

@@ -78,9 +78,9 @@ class DecodeGraphs:
         if self._pool is None:
             self._pool = torch.cuda.graph_pool_handle()
         before = counters.launches
-        # recorded steps of two and more sequences let each kernel be launched while the one before it
-        # still runs (measured: a gain there, a small loss for one sequence)
-        kernels.set_dependent_launch(size >= 2)
+        # a recorded step lets each kernel be launched while the one before it still runs: what a kernel reads
+        # that no kernel of the step writes (weights, positions, the cache of earlier steps) is on its way by then
+        kernels.set_dependent_launch(True)
         try:
             with torch.cuda.graph(cap.graph, pool=self._pool):
                 cap.logits = self.model.forward(ctx, self.cache, cap.want)

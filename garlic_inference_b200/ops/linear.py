@@ -6,9 +6,9 @@ Which product runs:
     result narrowed again.
   * bfloat16 weight of 256 MB and more (the head), 1 to 16 rows: this package's
     stream-K tcgen05 kernel, which cuts the weight evenly over the SMs.
-  * bfloat16 weight, one row: this package's bandwidth kernel (GEMV).
-  * bfloat16 weight, 2 to 8 rows: this package's tensor-core kernel for
-    decode batches, which reads the weight once.
+  * bfloat16 weight, 1 to 8 rows: this package's tensor-core kernel for
+    decode batches, which reads the weight once (or, when `GEMV_MAX_ROWS`
+    says so, the plain bandwidth kernel for one row).
   * bfloat16 weight, more rows: the library product (cuBLAS through
     `torch.mm`), float32 accumulation, or this package's tcgen05 kernel when
     `LARGE_GEMM` says so.  Upstream uses the same library for all
@@ -44,7 +44,12 @@ FUSED_SWIGLU_MIN_ROWS = int(os.environ.get("GARLIC_B200_FUSED_SWIGLU_ROWS", "512
 STREAMK_MIN_BYTES = int(os.environ.get("GARLIC_B200_STREAMK_MIN_BYTES", str(256 << 20)))
 
 STREAMK_MAX_ROWS = 16
-GEMV_MAX_ROWS = 1          # one row: the plain bandwidth kernel
+# Up to how many rows of x the plain bandwidth kernel (a warp per row of W) takes a product: none by default.
+# Alone it is as fast as the others at one row (175 us on the 1.24 GB head against 181 skinny and 183 stream-K),
+# but it gains nothing from being launched early behind its predecessor: a whole step of one sequence takes
+# 3.26 ms with the skinny and stream-K kernels, 3.29 ms with this kernel on the head only and 3.62 ms with it
+# everywhere.  GARLIC_B200_GEMV_ROWS=1 (or this variable) switches it on; the microbenchmark times it beside the others.
+GEMV_MAX_ROWS = int(os.environ.get("GARLIC_B200_GEMV_ROWS", "0"))
 SKINNY_MAX_ROWS = 8        # up to here: the tensor-core kernel that streams W once (it takes 16; the library is faster from 9 on)
 
 
@@ -63,11 +68,11 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
     if m == 0:
         return torch.empty((0, w.shape[0]), dtype=out_dtype, device=x.device)
     aligned = k % 8 == 0 and w.data_ptr() % 16 == 0 and x.data_ptr() % 16 == 0
+    if m <= GEMV_MAX_ROWS and aligned:
+        return kernels.gemv_bf16(x, w, out_dtype)
     if m <= STREAMK_MAX_ROWS and aligned and 0 < STREAMK_MIN_BYTES <= w.numel() * 2:
         return kernels.gemm_streamk_bf16(x, w, out_dtype)
     if m <= SKINNY_MAX_ROWS and aligned:
-        if m <= GEMV_MAX_ROWS:
-            return kernels.gemv_bf16(x, w, out_dtype)
         return kernels.gemm_skinny_bf16(x, w, out_dtype)
     kernels.require_gpu()
     if LARGE_GEMM == "tcgen05" and k % 8 == 0 and w.data_ptr() % 16 == 0 and x.data_ptr() % 16 == 0:
@@ -79,7 +84,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
 
 def swiglu_product(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
     """silu(x . Wg^T) * (x . Wu^T) for the packed weight [Wg; Wu]: prompts in bfloat16 run it as one tcgen05
-    kernel (product and activation), decode batches of 1 to 8 as one gemv or skinny kernel, everything else as the
+    kernel (product and activation), decode batches of 1 to 8 as one skinny (or gemv) kernel, everything else as the
     product of `linear` and the SwiGLU kernel."""
     m, k = x.shape
     if (FUSED_SWIGLU_MIN_ROWS > 0 and m >= FUSED_SWIGLU_MIN_ROWS and x.dtype == torch.bfloat16
@@ -88,7 +93,9 @@ def swiglu_product(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
         return kernels.gemm_tcgen05_swiglu_bf16(x, w_gate_up)
     if (0 < m <= SKINNY_MAX_ROWS and x.dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16
             and k % 8 == 0 and w_gate_up.shape[0] % 2 == 0 and x.data_ptr() % 16 == 0 and w_gate_up.data_ptr() % 16 == 0
-            and not (0 < STREAMK_MIN_BYTES <= w_gate_up.numel() * 2)):
+            and (m <= GEMV_MAX_ROWS or not (0 < STREAMK_MIN_BYTES <= w_gate_up.numel() * 2))):
         # decode batches: the activation in the product's last step
-        return kernels.gemv_swiglu_bf16(x, w_gate_up) if m <= GEMV_MAX_ROWS else kernels.gemm_skinny_swiglu_bf16(x, w_gate_up)
+        if m <= GEMV_MAX_ROWS:
+            return kernels.gemv_swiglu_bf16(x, w_gate_up)
+        return kernels.gemm_skinny_swiglu_bf16(x, w_gate_up)
     return kernels.swiglu(linear(x, w_gate_up))

@@ -213,3 +213,16 @@ def test_streamk_products_in_the_model(model_dirs, plain_cache, monkeypatch):
         got = tiny.run_trace_in_process(model, steps)
         tiny.assert_covers(got, reqs)
         tiny.compare(got, want, tiny.TOL["bfloat16"], "D bfloat16 with stream-K products")
+
+
+def test_gemv_products_in_the_model(model_dirs, plain_cache, monkeypatch):
+    """Steps of one sequence with the gemv kernels (plain and with the SwiGLU in it) taking every one-row product,
+    which by default the skinny and stream-K kernels take."""
+    import sys
+    from garlic_inference_b200 import AutoModel
+    monkeypatch.setattr(sys.modules["garlic_inference_b200.ops.linear"], "GEMV_MAX_ROWS", 1)
+    reqs, want = plain_cache("D")
+    model = AutoModel.from_pretrained(model_dirs("D"), device=0, dtype="bfloat16", max_tokens=2048, page_size=64)
+    got = tiny.run_trace_in_process(model, tiny.trace_tail_by_one(reqs, tail=32))
+    tiny.assert_covers(got, reqs)
+    tiny.compare(got, want, tiny.TOL["bfloat16"], "D bfloat16 with gemv products")
