@@ -115,6 +115,13 @@ __global__ void add_rmsnorm_vec_kernel(const T* __restrict__ delta, float* __res
             const int c = (it * blockDim.x + threadIdx.x) * 4;
             if (c < dim) w4[it] = load4_w(weight, w_dtype, c);
         }
+        // The residual was last written several kernels ago and the weights streamed since have pushed it out
+        // of L2: its lines are asked back into L2 now (a hint, nothing is read yet, so it does not matter
+        // whether that earlier kernel has finished).
+        if (!rows) {
+            const float* line = residual + (size_t)r * dim + threadIdx.x * 32;
+            if (threadIdx.x * 32 < dim) asm volatile("prefetch.global.L2 [%0];" ::"l"(line));
+        }
     }
     gi_pdl_wait();
     const size_t i = rows ? (size_t)rows[r] : (size_t)r;
