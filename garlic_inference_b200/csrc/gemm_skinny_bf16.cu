@@ -60,24 +60,6 @@ __device__ __forceinline__ void sk_step(float (&acc)[NT][4], const uint4& lo0, c
     }
 }
 
-// What the product can take over from the kernels around it (all pointers may be null):
-//  * rows of x that still lack a factor: x[m] stands for x[m] * rsqrt(sum_p in_ss[p * in_stride + m] * in_inv_dim
-//    + in_eps), the sums of squares coming in `in_parts` partial sums per row that are added in order.  The factor
-//    commutes with the product, so the CTA applies it to its sums at the end (before the SwiGLU, if there is one).
-//  * an output that goes to the residual stream and on to an RMSNorm: h = residual + bfloat16(product) is
-//    written back to `residual` (float32, [M, N]), h * norm_w goes to `out` as bfloat16 (the norm's rows before
-//    their factor) and the CTA's share of sum h^2 per row goes to out_ss[(tile * n_split + rank) * MP + m].
-// Together they are the residual add and the norm between two products without a kernel of their own.
-struct SkFuse {
-    const float* in_ss;
-    int in_parts, in_stride;
-    float in_inv_dim, in_eps;
-    float* residual;
-    const void* norm_w;
-    int norm_w_dtype;
-    float* out_ss;
-};
-
 // GLU: W is [2 I, K], a gate projection in its first I rows and an up projection in its last I.  A CTA then
 // takes R / 2 gate rows and the R / 2 up rows that belong to them, and writes silu(gate) * up, [M, I]
 // bfloat16: each factor rounded to bfloat16 as a stored product would be, then the SwiGLU kernel's float32
@@ -85,7 +67,7 @@ struct SkFuse {
 template <int NT, int WR, int WK, bool GLU>
 __global__ void __launch_bounds__(SK_THREADS)
 skinny_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, void* __restrict__ out, int out_f32,
-                   int M, int N, int K, int k_slice, SkFuse fuse) {
+                   int M, int N, int K, int k_slice) {
     static_assert(WR * WK == SK_WARPS, "8 warps");
     gi_pdl_launch_dependents();
     constexpr int MP = 8 * NT;                   // padded batch
@@ -95,7 +77,6 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, void*
     uint4* ring = reinterpret_cast<uint4*>(sk_smem);                     // [SK_DEPTH][CH][threads]: each thread's own queue
     float* red = reinterpret_cast<float*>(ring + SK_DEPTH * CH * SK_THREADS);   // [WK][MP][R]
     float* part = red + WK * MP * R;                                     // [MP][R], read by the cluster's other CTAs
-    float* row_scale = part + MP * R;                                    // [MP], the factors of x's rows
 
     cg::cluster_group cluster = cg::this_cluster();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
@@ -167,20 +148,9 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, void*
     };
 #pragma unroll
     for (int i = 0; i < SK_DEPTH - 1; ++i) issue(i);
-    if (fuse.residual && threadIdx.x < M * (R / 32) && row0 + (threadIdx.x % (R / 32)) * 32 < N)   // the tile's lines of the
-        asm volatile("prefetch.global.L2 [%0];"                                                     // residual: a hint only
-                     ::"l"(fuse.residual + (size_t)(threadIdx.x / (R / 32)) * N + row0 + (threadIdx.x % (R / 32)) * 32));
     gi_pdl_wait();                               // W is nobody's output: its first chunks are on their way by now
     uint4 x0[NT], x1[NT];
     load_x(0, x0, x1);
-    if (fuse.in_ss) {                            // a warp per row: the partial sums in order, 32 at a time
-        for (int m = warp; m < MP; m += SK_WARPS) {
-            float ss = 0.f;
-            for (int p = lane; p < fuse.in_parts; p += 32) ss += fuse.in_ss[(size_t)p * fuse.in_stride + m];
-            ss = warp_sum(ss);
-            if (lane == 0) row_scale[m] = rsqrtf(ss * fuse.in_inv_dim + fuse.in_eps);
-        }
-    }
     for (int i = 0; i < n_chunks; ++i) {
         issue(i + SK_DEPTH - 1);
         uint4 nx0[NT], nx1[NT];
@@ -227,7 +197,6 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, void*
                 gate += p[m * R + r];
                 up += p[m * R + r + half];
             }
-            if (fuse.in_ss) { gate *= row_scale[m]; up *= row_scale[m]; }
             const int col = blockIdx.x * half + r;
             if (m < M && col < inter) {
                 const float gf = __bfloat162float(__float2bfloat16_rn(gate)), uf = __bfloat162float(__float2bfloat16_rn(up));
@@ -241,34 +210,9 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, void*
             float v = 0.f;
             for (unsigned c = 0; c < n_ranks; ++c) v += n_ranks > 1 ? cluster.map_shared_rank(part, c)[i] : part[i];
             const int m = i / R, row = row0 + i % R;
-            if (fuse.in_ss) v *= row_scale[m];
-            float sq = 0.f;
             if (m < M && row < N) {
-                if (fuse.residual) {
-                    const size_t at = (size_t)m * N + row;
-                    const float h = fuse.residual[at] + __bfloat162float(__float2bfloat16_rn(v));
-                    fuse.residual[at] = h;
-                    reinterpret_cast<bf16*>(out)[at] = __float2bfloat16_rn(h * load_w(fuse.norm_w, fuse.norm_w_dtype, row));
-                    sq = h * h;
-                } else if (out_f32) {
-                    reinterpret_cast<float*>(out)[(size_t)m * N + row] = v;
-                } else {
-                    reinterpret_cast<bf16*>(out)[(size_t)m * N + row] = __float2bfloat16_rn(v);
-                }
-            }
-            if (fuse.residual) red[i] = sq;      // red is free by now: the sums of squares of this share, a row at a time below
-        }
-        if (fuse.residual) {
-            __syncthreads();
-            const int lo = rank * share;
-            for (int m = warp; m < MP; m += SK_WARPS) {
-                float ss = 0.f;
-                for (int r = lane; r < R; r += 32) {
-                    const int i = m * R + r;
-                    if (i >= lo && i < i_end) ss += red[i];
-                }
-                ss = warp_sum(ss);
-                if (lane == 0) fuse.out_ss[((size_t)blockIdx.x * n_ranks + rank) * MP + m] = ss;
+                if (out_f32) reinterpret_cast<float*>(out)[(size_t)m * N + row] = v;
+                else reinterpret_cast<bf16*>(out)[(size_t)m * N + row] = __float2bfloat16_rn(v);
             }
         }
     }
@@ -277,9 +221,9 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, void*
 
 template <int NT, int WR, int WK, bool GLU>
 static int launch_skinny(const bf16* x, const bf16* W, void* out, int out_f32, int M, int N, int K, int n_split,
-                         const SkFuse& fuse, cudaStream_t stream) {
+                         cudaStream_t stream) {
     constexpr int MP = 8 * NT, R = 16 * WR, KC = 64 * WK;
-    const size_t smem = (size_t)SK_DEPTH * 4 * SK_THREADS * 16 + (size_t)(WK + 1) * MP * R * sizeof(float) + MP * sizeof(float);
+    const size_t smem = (size_t)SK_DEPTH * 4 * SK_THREADS * 16 + (size_t)(WK + 1) * MP * R * sizeof(float);
     static bool attr_done = false;
     if (!attr_done) {
         cudaError_t e = cudaFuncSetAttribute((const void*)skinny_gemm_kernel<NT, WR, WK, GLU>,
@@ -302,17 +246,24 @@ static int launch_skinny(const bf16* x, const bf16* W, void* out, int out_f32, i
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = gi_pdl_enabled() ? 2 : 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, skinny_gemm_kernel<NT, WR, WK, GLU>, x, W, out, out_f32, M, N, K, k_slice, fuse);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, skinny_gemm_kernel<NT, WR, WK, GLU>, x, W, out, out_f32, M, N, K, k_slice);
     if (e != cudaSuccess) { gi_set_error("gi_gemm_skinny_bf16: launch: %s", cudaGetErrorString(e)); return (int)e; }
     return gi_check_launch("gi_gemm_skinny_bf16");
 }
 
-// The shape of a launch: 64-row tiles or 32-row ones, the CTAs of a cluster that share K, the tiles.
-struct SkShape { int wide, n_split; long long tiles; };
-
-// n_split: CTAs of a cluster that share K (1 to 8); 0 lets this function choose.
-// wide: 0 = 32 rows of W per CTA, 1 = 64 rows, -1 lets this function choose.
-static SkShape sk_shape(int N, int K, int n_split, int wide, int glu) {
+// n_split: CTAs of a cluster that share K (1 to 8); 0 lets the entry point choose.
+// wide: 0 = 32 rows of W per CTA, 1 = 64 rows, -1 lets the entry point choose.
+// glu: 0 = out[M, N]; 1 = W holds a gate and an up half and out is silu(gate) * up, [M, N / 2] bfloat16.
+static int skinny_entry(const void* x, const void* W, void* out, int out_dtype, int M, int N, int K, int n_split,
+                        int wide, int glu, void* stream) {
+    GI_REQUIRE(M >= 1 && M <= 16, "gi_gemm_skinny_bf16: %d rows; this kernel takes 1 to 16", M);
+    GI_REQUIRE(N > 0 && K > 0 && K % 8 == 0, "gi_gemm_skinny_bf16: inner size %d must be a positive multiple of 8", K);
+    GI_REQUIRE(((uintptr_t)x % 16 == 0) && ((uintptr_t)W % 16 == 0), "gi_gemm_skinny_bf16: operands must start on 16 bytes");
+    GI_REQUIRE(out_dtype == GI_DTYPE_BF16 || out_dtype == GI_DTYPE_F32, "gi_gemm_skinny_bf16: output dtype %d", out_dtype);
+    GI_REQUIRE(n_split >= 0 && n_split <= 8, "gi_gemm_skinny_bf16: a cluster of %d CTAs; 1 to 8 are possible", n_split);
+    GI_REQUIRE(wide >= -1 && wide <= 1, "gi_gemm_skinny_bf16: wide must be -1, 0 or 1");
+    GI_REQUIRE(!glu || (N % 2 == 0 && out_dtype == GI_DTYPE_BF16),
+               "gi_gemm_skinny_swiglu_bf16: W must hold a gate and an up half (%d rows) and the output be bfloat16", N);
     // Every CTA streams at the pace its own loads in flight allow, so the launch should fit the GPU in one
     // wave of equal CTAs (3 fit an SM) or be many waves long.  Among the shapes that fit in one wave, the
     // choice goes to slices of K of equal length (measured at 8 rows inside a decode step: hidden 4096 to 4096
@@ -343,29 +294,12 @@ static SkShape sk_shape(int N, int K, int n_split, int wide, int glu) {
         }
         wide = best_wide, n_split = best_split;
     }
-    const int R = wide ? 64 : 32;
-    return {wide, n_split, glu ? (N / 2 + R / 2 - 1) / (R / 2) : (N + R - 1) / R};
-}
-
-// glu: 0 = out[M, N]; 1 = W holds a gate and an up half and out is silu(gate) * up, [M, N / 2] bfloat16.
-static int skinny_entry(const void* x, const void* W, void* out, int out_dtype, int M, int N, int K, int n_split,
-                        int wide, int glu, const SkFuse& fuse, void* stream) {
-    GI_REQUIRE(M >= 1 && M <= 16, "gi_gemm_skinny_bf16: %d rows; this kernel takes 1 to 16", M);
-    GI_REQUIRE(N > 0 && K > 0 && K % 8 == 0, "gi_gemm_skinny_bf16: inner size %d must be a positive multiple of 8", K);
-    GI_REQUIRE(((uintptr_t)x % 16 == 0) && ((uintptr_t)W % 16 == 0), "gi_gemm_skinny_bf16: operands must start on 16 bytes");
-    GI_REQUIRE(out_dtype == GI_DTYPE_BF16 || out_dtype == GI_DTYPE_F32, "gi_gemm_skinny_bf16: output dtype %d", out_dtype);
-    GI_REQUIRE(n_split >= 0 && n_split <= 8, "gi_gemm_skinny_bf16: a cluster of %d CTAs; 1 to 8 are possible", n_split);
-    GI_REQUIRE(wide >= -1 && wide <= 1, "gi_gemm_skinny_bf16: wide must be -1, 0 or 1");
-    GI_REQUIRE(!glu || (N % 2 == 0 && out_dtype == GI_DTYPE_BF16),
-               "gi_gemm_skinny_swiglu_bf16: W must hold a gate and an up half (%d rows) and the output be bfloat16", N);
-    const SkShape shape = sk_shape(N, K, n_split, wide, glu);
-    n_split = shape.n_split, wide = shape.wide;
     const bf16* xp = (const bf16*)x;
     const bf16* wp = (const bf16*)W;
     const int f32 = out_dtype == GI_DTYPE_F32;
     cudaStream_t s = (cudaStream_t)stream;
-#define GI_SK(NT, WR, WK) (glu ? launch_skinny<NT, WR, WK, true>(xp, wp, out, f32, M, N, K, n_split, fuse, s) \
-                               : launch_skinny<NT, WR, WK, false>(xp, wp, out, f32, M, N, K, n_split, fuse, s))
+#define GI_SK(NT, WR, WK) (glu ? launch_skinny<NT, WR, WK, true>(xp, wp, out, f32, M, N, K, n_split, s) \
+                               : launch_skinny<NT, WR, WK, false>(xp, wp, out, f32, M, N, K, n_split, s))
     if (M <= 8) return wide ? GI_SK(1, 4, 2) : GI_SK(1, 2, 4);
     return wide ? GI_SK(2, 4, 2) : GI_SK(2, 2, 4);
 #undef GI_SK
@@ -373,41 +307,12 @@ static int skinny_entry(const void* x, const void* W, void* out, int out_dtype, 
 
 extern "C" int gi_gemm_skinny_bf16(const void* x, const void* W, void* out, int out_dtype, int M, int N, int K,
                                    int n_split, int wide, void* stream) {
-    return skinny_entry(x, W, out, out_dtype, M, N, K, n_split, wide, 0, SkFuse{}, stream);
+    return skinny_entry(x, W, out, out_dtype, M, N, K, n_split, wide, 0, stream);
 }
 
 // out[M, I] = silu(x . Wg^T) * (x . Wu^T) for W = [Wg; Wu] of two_inter = 2 I rows: the gate/up product of a
 // SwiGLU feed-forward at decode batches with the activation in the kernel's last step.
 extern "C" int gi_gemm_skinny_swiglu_bf16(const void* x, const void* W, void* out, int M, int two_inter, int K,
                                           int n_split, int wide, void* stream) {
-    return skinny_entry(x, W, out, GI_DTYPE_BF16, M, two_inter, K, n_split, wide, 1, SkFuse{}, stream);
-}
-
-// How many partial sums of squares per row, and with which stride between them, the product below leaves for
-// M rows of x against W[N, K]: what its out_ss has to hold (parts * stride floats).
-extern "C" int gi_gemm_skinny_norm_parts(int M, int N, int K, int* parts, int* stride) {
-    GI_REQUIRE(M >= 1 && M <= 16 && N > 0 && K > 0, "gi_gemm_skinny_norm_parts: sizes");
-    const SkShape shape = sk_shape(N, K, 0, -1, 0);
-    *parts = (int)(shape.tiles * shape.n_split);
-    *stride = M <= 8 ? 8 : 16;
-    return 0;
-}
-
-// The product with the norms around it (SkFuse above).  glu as above.  in_ss null: x is what it is; else its
-// rows still lack the factor rsqrt(sum of in_parts partial sums / in_dim + in_eps).  residual null: out is the
-// product ([M, N] or [M, N / 2] bfloat16); else (not with glu) residual += bfloat16(product), out = residual *
-// norm_w as bfloat16 and out_ss (sized by gi_gemm_skinny_norm_parts) takes the partial sums of residual^2.
-extern "C" int gi_gemm_skinny_fused_bf16(const void* x, const void* W, void* out, int M, int N, int K, int glu,
-                                         const float* in_ss, int in_parts, int in_stride, int in_dim, float in_eps,
-                                         float* residual, const void* norm_w, int norm_w_dtype, float* out_ss,
-                                         void* stream) {
-    GI_REQUIRE(!in_ss || (in_parts > 0 && in_stride >= (M <= 8 ? 8 : 16) && in_dim > 0),
-               "gi_gemm_skinny_fused_bf16: %d partial sums with stride %d for %d rows", in_parts, in_stride, M);
-    GI_REQUIRE(!residual || (!glu && norm_w && out_ss && (norm_w_dtype == GI_DTYPE_F32 || norm_w_dtype == GI_DTYPE_BF16)),
-               "gi_gemm_skinny_fused_bf16: the residual path needs norm weights and a place for the sums, and no SwiGLU");
-    SkFuse fuse = {};
-    fuse.in_ss = in_ss, fuse.in_parts = in_parts, fuse.in_stride = in_stride;
-    fuse.in_inv_dim = in_ss ? 1.f / (float)in_dim : 0.f, fuse.in_eps = in_eps;
-    fuse.residual = residual, fuse.norm_w = norm_w, fuse.norm_w_dtype = norm_w_dtype, fuse.out_ss = out_ss;
-    return skinny_entry(x, W, out, GI_DTYPE_BF16, M, N, K, 0, -1, glu, fuse, stream);
+    return skinny_entry(x, W, out, GI_DTYPE_BF16, M, two_inter, K, n_split, wide, 1, stream);
 }

@@ -255,59 +255,6 @@ def gemm_skinny_swiglu_bf16(x: torch.Tensor, w_gate_up: torch.Tensor, n_split: i
     return out
 
 
-_norm_parts: dict = {}
-
-
-def gemm_skinny_norm_parts(m: int, n: int, k: int) -> tuple[int, int]:
-    """(partial sums per row, floats between them) that `gemm_skinny_fused_bf16` leaves when its output goes on
-    to a norm: its `out_ss` holds parts * stride float32."""
-    key = (m > 8, n, k)
-    if key not in _norm_parts:
-        import ctypes
-        l = require_gpu()
-        parts, stride = ctypes.c_int(0), ctypes.c_int(0)
-        check(l.gi_gemm_skinny_norm_parts(m, n, k, ctypes.byref(parts), ctypes.byref(stride)), l)
-        counters.launches -= 1                    # a question, not a launch
-        _norm_parts[key] = (parts.value, stride.value)
-    return _norm_parts[key]
-
-
-def gemm_skinny_fused_bf16(x: torch.Tensor, w: torch.Tensor, glu: bool = False,
-                           in_ss: Optional[torch.Tensor] = None, in_dim: int = 0, in_eps: float = 0.0,
-                           residual: Optional[torch.Tensor] = None, norm_weight: Optional[torch.Tensor] = None):
-    """The skinny product (x [M<=16, K] . w[N,K]^T, bfloat16) with the norms around it taken in.
-
-    in_ss [parts, stride] float32: the rows of x still lack the factor rsqrt(sum of the partial sums of row m
-    / in_dim + in_eps); it is applied to the sums (before the SwiGLU when `glu`).
-    residual [M, N] float32 with norm_weight [N] (not with `glu`): residual += bfloat16(product) in place, and
-    the return value is (residual * norm_weight as bfloat16 [M, N], partial sums of residual^2 [parts, stride]):
-    the rows of the following RMSNorm before their factor.  Otherwise the product is returned ([M, N], or
-    [M, N / 2] after the SwiGLU)."""
-    l = require_gpu()
-    _dense(x, "x", torch.bfloat16), _dense(w, "w", torch.bfloat16)
-    (m, k), (n, k2) = x.shape, w.shape
-    if k != k2:
-        raise KernelError(f"inner sizes differ: x {tuple(x.shape)}, w {tuple(w.shape)}")
-    in_parts = in_stride = 0
-    if in_ss is not None:
-        _dense(in_ss, "in_ss", torch.float32)
-        in_parts, in_stride = in_ss.shape
-    out_ss = None
-    if residual is not None:
-        _dense(residual, "residual", torch.float32), _dense(norm_weight, "norm_weight")
-        if glu or tuple(residual.shape) != (m, n) or norm_weight.numel() != n:
-            raise KernelError(f"residual {tuple(residual.shape)} / norm weight {tuple(norm_weight.shape)} do not fit "
-                              f"a product of {m} x {n}" + (" with a SwiGLU" if glu else ""))
-        parts, stride = gemm_skinny_norm_parts(m, n, k)
-        out_ss = torch.empty((parts, stride), dtype=torch.float32, device=x.device)
-    out = torch.empty((m, n // 2 if glu else n), dtype=torch.bfloat16, device=x.device)
-    check(l.gi_gemm_skinny_fused_bf16(_ptr(x), _ptr(w), _ptr(out), m, n, k, int(glu), _ptr(in_ss), in_parts, in_stride,
-                                      int(in_dim), float(in_eps), _ptr(residual), _ptr(norm_weight),
-                                      code(norm_weight.dtype) if norm_weight is not None else 0, _ptr(out_ss),
-                                      _stream()), l)
-    return (out, out_ss) if residual is not None else out
-
-
 _tcgen05_flag: dict = {}
 
 

@@ -43,8 +43,6 @@ _SIGNATURES = {
     "gi_gemm_skinny_bf16": ([P, P, P, I, I, I, I, I, I, P], I),
     "gi_gemv_swiglu_bf16": ([P, P, P, I, I, P], I),
     "gi_gemm_skinny_swiglu_bf16": ([P, P, P, I, I, I, I, I, P], I),
-    "gi_gemm_skinny_norm_parts": ([I, I, I, P, P], I),
-    "gi_gemm_skinny_fused_bf16": ([P, P, P, I, I, I, I, P, I, I, I, F, P, P, I, P, P], I),
     "gi_gemm_tcgen05_swiglu_bf16": ([P, P, P, I, I, I, P, P], I),
     "gi_gemm_streamk_bf16": ([P, P, P, I, I, I, I, P, P, P, P], I),
     "gi_gemm_streamk_workspace_floats": ([], L),

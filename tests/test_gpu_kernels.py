@@ -180,50 +180,6 @@ def test_gemm_skinny_swiglu_bf16(m, inter, k, split, wide):
     torch.testing.assert_close(fused.float(), gate / (1 + torch.exp(-gate)) * up, rtol=3e-2, atol=3e-2)
 
 
-@pytest.mark.parametrize("m,hidden,inner,wide_out,glu", [(8, 4096, 4096, 6144, False), (3, 96, 200, 130, False),
-                                                         (1, 1000, 72, 48, True), (13, 264, 520, 96, False),
-                                                         (8, 4096, 12288, 24576, True), (5, 40, 64, 34, True)])
-@pytest.mark.parametrize("w_dtype", [torch.bfloat16, torch.float32])
-def test_gemm_skinny_with_the_norms_around_it(m, hidden, inner, wide_out, glu, w_dtype):
-    """residual += x . W1^T, RMSNorm, . W2^T (with or without a SwiGLU) as two products and no kernel between them:
-    the first leaves the norm's rows before their factor and partial sums of squares, the second applies the
-    factor to its sums.  Against the three kernels one after the other and against float32 arithmetic."""
-    g = torch.Generator(device=DEV).manual_seed(m + hidden + inner)
-    x = torch.randn(m, inner, generator=g, device=DEV).to(torch.bfloat16)
-    w1 = (torch.randn(hidden, inner, generator=g, device=DEV) / math.sqrt(inner)).to(torch.bfloat16)
-    w2 = (torch.randn(wide_out, hidden, generator=g, device=DEV) / math.sqrt(hidden)).to(torch.bfloat16)
-    norm_w = (1 + 0.3 * torch.randn(hidden, generator=g, device=DEV)).to(w_dtype)
-    residual0 = torch.randn(m, hidden, generator=g, device=DEV) * 3
-    eps = 1e-5
-
-    residual = residual0.clone()
-    rows, sums = K().gemm_skinny_fused_bf16(x, w1, residual=residual, norm_weight=norm_w)
-    out = K().gemm_skinny_fused_bf16(rows, w2, glu=glu, in_ss=sums, in_dim=hidden, in_eps=eps)
-
-    # step by step with this library's kernels
-    delta = K().gemm_skinny_bf16(x, w1, torch.bfloat16)
-    want_residual = residual0.clone()
-    normed = K().add_rmsnorm(delta, want_residual, norm_w, eps, torch.bfloat16)
-    assert torch.equal(residual, want_residual), "the residual stream takes the same sum"
-    torch.testing.assert_close(sums.sum(0)[:m], (want_residual ** 2).sum(1), rtol=1e-5, atol=1e-5)
-    assert float(sums[:, m:].abs().sum()) == 0, "rows beyond the batch add nothing"
-    stepwise = K().gemm_skinny_swiglu_bf16(normed, w2) if glu else K().gemm_skinny_bf16(normed, w2, torch.bfloat16)
-    assert out.shape == stepwise.shape
-    torch.testing.assert_close(out.float(), stepwise.float(), rtol=3e-2, atol=3e-2)
-
-    # float32 arithmetic
-    h = residual0 + (x.float() @ w1.float().T).to(torch.bfloat16).float()
-    n32 = h * torch.rsqrt((h * h).mean(1, keepdim=True) + eps) * norm_w.float()
-    y = n32 @ w2.float().T
-    if glu:
-        gate, up = y[:, :wide_out // 2], y[:, wide_out // 2:]
-        y = gate / (1 + torch.exp(-gate)) * up
-    torch.testing.assert_close(out.float(), y, rtol=3e-2, atol=3e-2)
-    again_res = residual0.clone()
-    rows2, sums2 = K().gemm_skinny_fused_bf16(x, w1, residual=again_res, norm_weight=norm_w)
-    assert torch.equal(rows, rows2) and torch.equal(sums, sums2), "same bits from run to run"
-
-
 @pytest.mark.parametrize("m,n,k", [(1, 128, 64), (8, 100, 1000), (5, 264, 4096), (16, 4096, 4096), (8, 24576, 512), (3, 777, 72),
                                    (8, 4096, 12288), (2, 151936, 256), (13, 6144, 4096)])
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
