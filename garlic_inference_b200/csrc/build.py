@@ -35,6 +35,12 @@ class BuildError(RuntimeError):
     pass
 
 
+def timeline_build() -> bool:
+    """GARLIC_B200_TIMELINE=1: a build of its own (folder `_build_timeline`) whose kernels note when they start
+    and when they are released (common.cuh); `python -m garlic_inference_b200.ops.microbench timeline` reads it."""
+    return os.environ.get("GARLIC_B200_TIMELINE", "0") == "1"
+
+
 def sources() -> list[Path]:
     return sorted(CSRC.glob("*.cu"))
 
@@ -59,6 +65,7 @@ def _fingerprint() -> str:
         h.update(p.name.encode())
         h.update(p.read_bytes())
     h.update(" ".join(NVCC_FLAGS).encode())
+    h.update(b"timeline" if timeline_build() else b"")
     return h.hexdigest()
 
 
@@ -68,7 +75,7 @@ def _build_dir() -> Path:
         d = Path(override)
         d.mkdir(parents=True, exist_ok=True)
         return d
-    d = CSRC / "_build"
+    d = CSRC / ("_build_timeline" if timeline_build() else "_build")
     try:
         d.mkdir(exist_ok=True)
         probe = d / f".w{os.getpid()}"
@@ -76,7 +83,7 @@ def _build_dir() -> Path:
         probe.unlink()
         return d
     except OSError:
-        d = Path(tempfile.gettempdir()) / f"garlic_b200_build_{os.getuid()}"
+        d = Path(tempfile.gettempdir()) / f"garlic_b200_build_{os.getuid()}{'_timeline' if timeline_build() else ''}"
         d.mkdir(parents=True, exist_ok=True)
         return d
 
@@ -86,7 +93,8 @@ def _say(msg: str) -> None:
 
 
 def _compile_one(nvcc: str, src: Path, obj: Path, extra: list[str]) -> None:
-    cmd = [nvcc, *NVCC_FLAGS, *extra, "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
+    tl = ["-DGI_TIMELINE", f"-DGI_TU={src.stem}"] if timeline_build() else []
+    cmd = [nvcc, *NVCC_FLAGS, *tl, *extra, "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
     t0 = time.time()
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:

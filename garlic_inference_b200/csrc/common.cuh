@@ -37,6 +37,36 @@ int gi_check_launch(const char* what);
 
 typedef __nv_bfloat16 bf16;
 
+// A timeline of a recorded step, for builds made with -DGI_TIMELINE -DGI_TU=<file stem> (csrc/build.py does
+// that when GARLIC_B200_TIMELINE=1; the ordinary build has none of it).  Thread 0 of block 0 of every kernel
+// notes %globaltimer twice: when it starts (mark 0, with the launch's size) and when the kernel before it in the
+// stream has finished (mark 1, after griddepcontrol.wait).  Both marks are taken in launch order, so entry i of
+// either list belongs to the i-th kernel, and the time between the second marks of two neighbours is what the
+// earlier one costs the chain.  Layout of the buffer (unsigned 64-bit): [0] and [1] count the marks, entry i is
+// [4 + 4 i + {0: start ns, 1: released ns, 2: blocks << 16 | threads}].  Every file has its own copy of the
+// pointer, set through gi_tl_set_<file stem>().
+#ifdef GI_TIMELINE
+#define GI_TL_ENTRIES 4096
+static __device__ unsigned long long* gi_tl_buf = nullptr;
+#define GI_TL_CAT2(a, b) a##b
+#define GI_TL_CAT(a, b) GI_TL_CAT2(a, b)
+extern "C" void GI_TL_CAT(gi_tl_set_, GI_TU)(void* p) { cudaMemcpyToSymbol(gi_tl_buf, &p, sizeof(p)); }
+__device__ __forceinline__ void gi_tl_mark(int which) {
+    if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && gi_tl_buf) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        const unsigned long long i = atomicAdd(gi_tl_buf + which, 1ULL);
+        if (i < GI_TL_ENTRIES) {
+            gi_tl_buf[4 + 4 * i + which] = t;
+            if (which == 0)
+                gi_tl_buf[4 + 4 * i + 2] = ((unsigned long long)(gridDim.x * gridDim.y * gridDim.z) << 16) | blockDim.x;
+        }
+    }
+}
+#else
+__device__ __forceinline__ void gi_tl_mark(int) {}
+#endif
+
 // Programmatic dependent launch.  Every kernel of this library starts with gi_pdl_start(): when the
 // launches carry the attribute below, it lets the next kernel of the stream be launched while this one
 // still runs (its blocks then sit in their own gi_pdl_start until this grid has finished and its writes
@@ -46,16 +76,22 @@ typedef __nv_bfloat16 bf16;
 // steps): batch 8 +7 %, batch 1 +11 %, batch 64 +1 %.  The engine asks for it (gi_set_pdl) while it records
 // decode steps, and nowhere else; GARLIC_B200_PDL=0 or =1 in the environment overrides that for the process.
 __device__ __forceinline__ void gi_pdl_start() {
+    gi_tl_mark(0);
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    gi_tl_mark(1);
 }
 // The two halves apart, for kernels that have something to do that depends on no earlier kernel (fetching
 // weights): gi_pdl_launch_dependents() first, then that work, then gi_pdl_wait() before anything an
 // earlier kernel wrote is read and before anything is written.
 __device__ __forceinline__ void gi_pdl_launch_dependents() {
+    gi_tl_mark(0);
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
-__device__ __forceinline__ void gi_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void gi_pdl_wait() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    gi_tl_mark(1);
+}
 
 // kernel<<<grid, block, smem, stream>>>(args...), with the attribute that allows the overlap above when
 // gi_pdl_enabled().

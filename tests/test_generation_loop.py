@@ -216,3 +216,17 @@ def test_one_step_ahead_respects_the_position_limit():
     out = lp.run([[1, 2, 3]], GenParams(max_new_tokens=10))
     assert out == [[4, 5]]                        # 3 + 2 = 5 positions
     assert st.live == {} and max(len(c) for c in st.ahead_calls) == 1 and len(st.ahead_calls) == 1
+
+
+def test_timeline_finds_the_repeating_layer():
+    """The timeline's reading of its marks: entries in launch order, and the period of the launch sizes."""
+    import torch
+    from garlic_inference_b200.engine import timeline
+    head, layer, tail = [(1, 32)], [(8, 256), (384, 256), (96, 128), (256, 160)], [(148, 192), (8, 32)]
+    assert timeline.period(head + layer * 12 + tail) == 4
+    assert timeline.period([(i, 32) for i in range(40)]) == 0
+    buf = torch.zeros(4 + 4 * timeline.ENTRIES, dtype=torch.int64)
+    buf[0], buf[1] = 2, 2
+    buf[4:8] = torch.tensor([1000, 1500, (3 << 16) | 128, 0])
+    buf[8:12] = torch.tensor([2000, 4500, (7 << 16) | 64, 0])
+    assert timeline.read(buf) == [(3, 128, 0.0, 0.5), (7, 64, 1.0, 3.5)]
