@@ -2,6 +2,7 @@
 
     python -m garlic_inference_b200.ops.microbench run  OP M [SHAPE]     a few plain launches (what ncu captures)
     python -m garlic_inference_b200.ops.microbench time [linear|attn|prefill|small]   GPU time inside CUDA graphs, cold L2
+    python -m garlic_inference_b200.ops.microbench time attn_long    the attention kernels at 8,192 to 32,768 tokens
 
 OP: gemv | skinny | streamk | cublas | tcgen05 (M = rows of x, SHAPE = qkv | o | gate_up | down | lm_head at Qwen3-8B sizes),
 attn_decode and attn_decode_tcgen05 (M = sequences, 2,048 cached tokens each), attn_prefill and attn_prefill_tcgen05 (M = prompt length).
@@ -145,6 +146,32 @@ def time_attention() -> None:
             del pools
 
 
+def time_attention_long() -> None:
+    """The tcgen05 attention kernels beyond the benchmark's lengths: decode over 8,192 to 32,768 cached tokens at
+    small batches (the slices are the ones the engine picks for the batch), one prompt of 8,192 and of 16,384 tokens."""
+    for batch in (1, 2, 4, 8):
+        for ctx in (8192, 16384, 32768):
+            nbytes = batch * ctx * N_KV * HEAD_DIM * 2 * 2
+            copies = min(40, max(3, int(500e6 // nbytes) + 1))
+            pools, table, q, pos, slot = _decode_case(batch, ctx, copies)
+            ms = graph_time([(lambda p=p: kernels.attention_decode_tcgen05(q, p[0], p[1], table, pos, slot,
+                                                                           HEAD_DIM ** -0.5, 0)) for p in pools])
+            print(f"attn_decode batch={batch:3d} ctx={ctx:6d}  tcgen05 {ms * 1e3:7.1f} us  {nbytes / ms / 1e6:5.0f} GB/s  "
+                  f"({kernels.decode_splits_tcgen05(batch, N_KV)} slices)", flush=True)
+            del pools
+    for m in (8192, 16384):
+        n_pages = m // PAGE
+        k_pool = torch.randn(n_pages, N_KV, PAGE, HEAD_DIM, device=DEV, dtype=torch.bfloat16)
+        v_pool = torch.randn_like(k_pool)
+        table = torch.arange(n_pages, dtype=torch.int32, device=DEV).view(1, -1)
+        q = torch.randn(m, N_Q, HEAD_DIM, device=DEV, dtype=torch.bfloat16)
+        tiles = torch.tensor([(0, r, 128, r) for r in reversed(range(0, m, 128))], dtype=torch.int32, device=DEV)
+        ms = graph_time([lambda: kernels.attention_prefill_tcgen05(q, k_pool, v_pool, table, tiles, HEAD_DIM ** -0.5, 0)] * 3)
+        flops = 4 * N_Q * HEAD_DIM * m * (m + 128) / 2
+        print(f"attention prompt of {m}  tcgen05 {ms * 1e3:8.1f} us  {flops / ms / 1e9:5.0f} TFLOP/s", flush=True)
+    print("error flag", int(kernels.tcgen05_error_flag(DEV).item()))
+
+
 def time_small(hidden: int = 4096, inter: int = 12288) -> None:
     """The kernels between the products of a decode step, 32 calls back to back in a graph on operands
     that stay in L2 (as they do in a step, where the kernel before has just written them)."""
@@ -241,6 +268,8 @@ def main(argv) -> int:
             time_prefill_linear()
         if which in ("all", "small"):
             time_small()
+        if which == "attn_long":
+            time_attention_long()
     else:
         print(__doc__)
         return 2
