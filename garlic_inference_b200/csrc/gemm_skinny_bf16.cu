@@ -1,4 +1,4 @@
-// bfloat16 product for decode batches: out[M,N] = x[M,K] . W[N,K]^T with 2 <= M <= 16.
+// bfloat16 product for decode batches: out[M,N] = x[M,K] . W[N,K]^T with 1 <= M <= 16.
 //
 // At these sizes the step is bound by reading W once, but a plain GEMV has
 // too much arithmetic and activation traffic per weight byte once M grows, so

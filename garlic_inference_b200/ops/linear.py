@@ -40,7 +40,7 @@ FUSED_SWIGLU_MIN_ROWS = int(os.environ.get("GARLIC_B200_FUSED_SWIGLU_ROWS", "512
 # Which kernel takes bfloat16 products of 1 to 16 rows whose weight has at least this many bytes: the stream-K
 # tcgen05 kernel (W cut evenly over the SMs, 6.6 TB/s once it runs but about 10 us to start and to merge the
 # cut tiles).  Measured at 8 rows: 189 against 216 us on the 1.24 GB head, 39.4 against 38.9 us on 201 MB,
-# 27.8 against 22.8 us on 101 MB; so smaller weights stay with the gemv / skinny kernels.  0 switches it off.
+# 27.8 against 22.8 us on 101 MB; so smaller weights stay with the skinny kernel.  0 switches it off.
 STREAMK_MIN_BYTES = int(os.environ.get("GARLIC_B200_STREAMK_MIN_BYTES", str(256 << 20)))
 
 STREAMK_MAX_ROWS = 16
