@@ -1,16 +1,17 @@
 // bfloat16 product for decode batches on the fifth-generation tensor cores, with the weight matrix
-// cut evenly over the SMs: out[M,N] = x[M,K] . W[N,K]^T for 1 <= M <= 16.
+// cut evenly over the SMs: out[M,N] = x[M,K] . W[N,K]^T for 1 <= M <= 64.
 //
 // A decode step is bound by reading W once, so what matters is that every SM streams the same share
 // of W without a pause.  The work is the list of (128 rows of W) x (64 of K) blocks, tile after tile;
 // CTA c of G (one per SM) takes the blocks [c U / G, (c + 1) U / G) of the U blocks in that order, whatever
 // the shape is.  Its range is at most the tail of one tile, some whole tiles, and the head of one tile:
-//   warp 0, one lane:  TMA.  Block after block, 128 x 64 of W (16 KB) and the 16 x 64 of x that go with
-//                      it (2 KB, rows beyond M zero-filled) into a ring of ten shared-memory stages (six when
-//                      every CTA takes one whole tile, see the entry point).
+//   warp 0, one lane:  TMA.  Block after block, 128 x 64 of W (16 KB) and the BN x 64 of x that go with
+//                      it (BN = 16, 32 or 64 rows, the batch rounded up; rows beyond M zero-filled) into a
+//                      ring of shared-memory stages (nine or ten; four to six when every CTA takes one whole
+//                      tile, see the entry point).
 //   warp 1, one lane:  MMA.  The operands are swapped: the 128 rows of W are the 128-row operand of
-//                      tcgen05.mma, the batch is the 16-wide one; a tile's part accumulates in one of two
-//                      accumulators of 16 columns in tensor memory.
+//                      tcgen05.mma, the batch is the BN-wide one; a tile's part accumulates in one of two
+//                      accumulators of BN columns in tensor memory.
 //   warps 2..5:        epilogue.  A whole tile is stored; the tail of a tile (its head belongs to the CTA
 //                      before) goes as float32 to this CTA's slot of a work space, followed by a flag;
 //                      the head of a tile (the CTA's last part) waits for the flags of the CTAs after it that
@@ -28,16 +29,17 @@
 
 #define SKT_ROWS 128                    // rows of W per tile
 #define SKT_BK 64
-#define SKT_BN 16                       // the batch, padded
-#define SKT_MAX_STAGES 10               // 180 KB of ring: 160 KB of W in flight per SM, one CTA per SM (the cut-evenly mode)
-#define SKT_FEW_STAGES 6                // 108 KB: two CTAs per SM (the mode of one whole tile per CTA)
+#define SKT_MAX_BN 64                   // the widest batch (padded) a launch takes; narrower ones use 16 or 32
+#define SKT_MAX_STAGES 10               // the cut-evenly mode, one CTA per SM: 10 stages of 18 or 20 KB, 9 of 24 KB
 #define SKT_THREADS 192
 #define SKT_W_BYTES (SKT_ROWS * SKT_BK * 2)
-#define SKT_X_BYTES (SKT_BN * SKT_BK * 2)
-#define SKT_TMEM_COLS 32                // two accumulators of 16 columns
 #define SKT_SPIN_LIMIT (1 << 22)
 #define SKT_MAX_CTAS 256
-#define SKT_SLOT_FLOATS (SKT_BN * SKT_ROWS)
+#define SKT_SLOT_FLOATS (SKT_MAX_BN * SKT_ROWS)      // a CTA's slot of the work space, whatever the batch
+// stages of the ring: as many as fit one CTA per SM, or two CTAs per SM (the mode of one whole tile per CTA)
+constexpr int skt_stages(int bn, bool whole_tiles) {
+    return whole_tiles ? (bn == 16 ? 6 : bn == 32 ? 5 : 4) : (bn == 64 ? 9 : 10);
+}
 
 #define SKT_ERR_PRODUCER 31
 #define SKT_ERR_MMA 32
@@ -123,11 +125,13 @@ __device__ __forceinline__ SktSegment skt_segment(long long u, long long u1, int
     return s;
 }
 
-template <int OUT_F32, int SKT_STAGES>
+template <int OUT_F32, int SKT_STAGES, int BN>
 __global__ void __launch_bounds__(SKT_THREADS, 1)
 gemm_streamk_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                             void* __restrict__ out, float* __restrict__ partials, int* __restrict__ flags,
                             int M, int N, int K, int* __restrict__ error_flag) {
+    constexpr int SKT_X_BYTES = BN * SKT_BK * 2;
+    constexpr int SKT_TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;       // two accumulators of BN columns
     gi_pdl_launch_dependents();
     extern __shared__ unsigned char skt_raw[];
     unsigned char* smem = (unsigned char*)(((uintptr_t)skt_raw + 1023) & ~(uintptr_t)1023);
@@ -215,8 +219,8 @@ gemm_streamk_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __g
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            // float32 accumulate, bfloat16 operands, both K-major, N = 16 (the batch), M = 128 (rows of W)
-            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(SKT_BN >> 3) << 17) | ((uint32_t)(SKT_ROWS >> 4) << 24);
+            // float32 accumulate, bfloat16 operands, both K-major, N = BN (the batch), M = 128 (rows of W)
+            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(SKT_ROWS >> 4) << 24);
             int it = 0, local = 0;
             bool ok = true;
             for (long long u = u0; u < u1 && ok; ++local) {
@@ -227,7 +231,7 @@ gemm_streamk_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __g
                     break;
                 }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t acc = tmem + buf * SKT_BN;
+                const uint32_t acc = tmem + buf * BN;
                 for (int kt = sg.ka; kt < sg.kb; ++kt, ++it) {
                     const int s = it % SKT_STAGES;
                     if (!skt_mbar_wait(&ctl->full[s], (it / SKT_STAGES) & 1, abort)) {
@@ -260,8 +264,14 @@ gemm_streamk_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __g
                 break;
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            float v[16];
-            skt_ld16(tmem + ((uint32_t)(q * 32) << 16) + buf * SKT_BN, v);
+            float v[BN];
+#pragma unroll
+            for (int part = 0; part < BN / 16; ++part) {
+                float piece[16];
+                skt_ld16(tmem + ((uint32_t)(q * 32) << 16) + buf * BN + part * 16, piece);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) v[part * 16 + i] = piece[i];
+            }
             // the accumulator is in registers: the MMA lane may overwrite it
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
@@ -271,7 +281,7 @@ gemm_streamk_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __g
                 // the tail of a tile whose head another CTA holds: float32 to this CTA's slot, then the flag
                 float* slot = partials + (size_t)c * SKT_SLOT_FLOATS;
 #pragma unroll
-                for (int m = 0; m < 16; ++m) slot[m * SKT_ROWS + row_in_tile] = v[m];
+                for (int m = 0; m < BN; ++m) slot[m * SKT_ROWS + row_in_tile] = v[m];
                 __threadfence();
                 skt_epilogue_any(false);
                 if (threadIdx.x == 64) asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(flags + c), "r"(1) : "memory");
@@ -303,7 +313,7 @@ gemm_streamk_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __g
                         for (int j = 0; j < n_after; ++j) {              // added in CTA order: one order of summation
                             const float* slot = partials + (size_t)(c + 1 + j) * SKT_SLOT_FLOATS;
 #pragma unroll
-                            for (int m = 0; m < 16; ++m) v[m] += __ldcg(slot + m * SKT_ROWS + row_in_tile);
+                            for (int m = 0; m < BN; ++m) v[m] += __ldcg(slot + m * SKT_ROWS + row_in_tile);
                         }
                         skt_epilogue_any(false);                         // all four warps have read the slots
                         for (int j = (int)(threadIdx.x - 64); j < n_after; j += 128) flags[c + 1 + j] = 0;   // for the next launch
@@ -315,12 +325,12 @@ gemm_streamk_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __g
                         if (OUT_F32) {
                             float* o = reinterpret_cast<float*>(out);
 #pragma unroll
-                            for (int m = 0; m < 16; ++m)
+                            for (int m = 0; m < BN; ++m)
                                 if (m < M) o[(size_t)m * N + row] = v[m];
                         } else {
                             bf16* o = reinterpret_cast<bf16*>(out);
 #pragma unroll
-                            for (int m = 0; m < 16; ++m)
+                            for (int m = 0; m < BN; ++m)
                                 if (m < M) o[(size_t)m * N + row] = __float2bfloat16_rn(v[m]);
                         }
                     }
@@ -385,9 +395,26 @@ static bool gi_streamk_whole_tiles_enabled() {
 extern "C" long long gi_gemm_streamk_workspace_floats(void) { return (long long)SKT_MAX_CTAS * SKT_SLOT_FLOATS; }
 extern "C" int gi_gemm_streamk_flags(void) { return SKT_MAX_CTAS; }
 
+template <int OUT_F32, bool WHOLE, int BN>
+static int skt_launch(const CUtensorMap& map_w, const CUtensorMap& map_x, void* out, float* partials, int* flags, int M, int N,
+                      int K, long long g, int* error_flag, cudaStream_t stream) {
+    constexpr int stages = skt_stages(BN, WHOLE);
+    const size_t smem = (size_t)stages * (SKT_W_BYTES + BN * SKT_BK * 2) + sizeof(SktControl) + 1024;
+    static bool attr_done = false;
+    if (!attr_done) {
+        cudaError_t e = cudaFuncSetAttribute((const void*)gemm_streamk_tcgen05_kernel<OUT_F32, stages, BN>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) { gi_set_error("gi_gemm_streamk_bf16: shared memory: %s", cudaGetErrorString(e)); return (int)e; }
+        attr_done = true;
+    }
+    gi_launch(gemm_streamk_tcgen05_kernel<OUT_F32, stages, BN>, dim3((unsigned)g), dim3(SKT_THREADS), smem, stream, map_w, map_x,
+              out, partials, flags, M, N, K, error_flag);
+    return gi_check_launch("gi_gemm_streamk_bf16");
+}
+
 extern "C" int gi_gemm_streamk_bf16(const void* x, const void* W, void* out, int out_dtype, int M, int N, int K,
                                     float* partials, int* flags, int* error_flag, void* stream) {
-    GI_REQUIRE(M >= 1 && M <= SKT_BN, "gi_gemm_streamk_bf16: %d rows; this kernel takes 1 to 16", M);
+    GI_REQUIRE(M >= 1 && M <= SKT_MAX_BN, "gi_gemm_streamk_bf16: %d rows; this kernel takes 1 to %d", M, SKT_MAX_BN);
     GI_REQUIRE(N > 0 && K > 0 && K % 8 == 0, "gi_gemm_streamk_bf16: inner size %d must be a positive multiple of 8", K);
     GI_REQUIRE(((uintptr_t)x % 16 == 0) && ((uintptr_t)W % 16 == 0), "gi_gemm_streamk_bf16: operands must start on 16 bytes");
     GI_REQUIRE(out_dtype == GI_DTYPE_BF16 || out_dtype == GI_DTYPE_F32, "gi_gemm_streamk_bf16: output dtype %d", out_dtype);
@@ -407,24 +434,16 @@ extern "C" int gi_gemm_streamk_bf16(const void* x, const void* W, void* out, int
     const bool whole_tiles = n_tiles >= n_sm && n_tiles <= 2LL * n_sm && gi_streamk_whole_tiles_enabled();
     long long g = whole_tiles ? n_tiles : (units < n_sm ? units : n_sm);   // cut mode: all CTAs resident at once, they wait for one another
     if (!whole_tiles && g > SKT_MAX_CTAS) g = SKT_MAX_CTAS;
+    const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
     CUtensorMap map_w, map_x;
     if (int rc = skt_make_map(&map_w, W, N, K, SKT_ROWS)) return rc;
-    if (int rc = skt_make_map(&map_x, x, M, K, SKT_BN)) return rc;
-    const int stages = whole_tiles ? SKT_FEW_STAGES : SKT_MAX_STAGES;
-    const size_t smem = (size_t)stages * (SKT_W_BYTES + SKT_X_BYTES) + sizeof(SktControl) + 1024;
+    if (int rc = skt_make_map(&map_x, x, M, K, bn)) return rc;
     const int f32 = out_dtype == GI_DTYPE_F32;
-    static bool attr_done[2][2] = {{false, false}, {false, false}};
-    const void* fn = f32 ? (whole_tiles ? (const void*)gemm_streamk_tcgen05_kernel<1, SKT_FEW_STAGES> : (const void*)gemm_streamk_tcgen05_kernel<1, SKT_MAX_STAGES>)
-                         : (whole_tiles ? (const void*)gemm_streamk_tcgen05_kernel<0, SKT_FEW_STAGES> : (const void*)gemm_streamk_tcgen05_kernel<0, SKT_MAX_STAGES>);
-    if (!attr_done[f32][whole_tiles]) {
-        cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) { gi_set_error("gi_gemm_streamk_bf16: shared memory: %s", cudaGetErrorString(e)); return (int)e; }
-        attr_done[f32][whole_tiles] = true;
-    }
-#define SKT_LAUNCH(F, S) gi_launch(gemm_streamk_tcgen05_kernel<F, S>, dim3((unsigned)g), dim3(SKT_THREADS), smem, (cudaStream_t)stream, \
-                                   map_w, map_x, out, partials, flags, M, N, K, error_flag)
-    if (f32) { if (whole_tiles) SKT_LAUNCH(1, SKT_FEW_STAGES); else SKT_LAUNCH(1, SKT_MAX_STAGES); }
-    else { if (whole_tiles) SKT_LAUNCH(0, SKT_FEW_STAGES); else SKT_LAUNCH(0, SKT_MAX_STAGES); }
-#undef SKT_LAUNCH
-    return gi_check_launch("gi_gemm_streamk_bf16");
+    cudaStream_t s = (cudaStream_t)stream;
+#define SKT_GO(F, WH, B) return skt_launch<F, WH, B>(map_w, map_x, out, partials, flags, M, N, K, g, error_flag, s)
+#define SKT_PICK_BN(F, WH) { if (bn == 16) SKT_GO(F, WH, 16); if (bn == 32) SKT_GO(F, WH, 32); SKT_GO(F, WH, 64); }
+    if (f32) { if (whole_tiles) SKT_PICK_BN(1, true) else SKT_PICK_BN(1, false) }
+    else { if (whole_tiles) SKT_PICK_BN(0, true) else SKT_PICK_BN(0, false) }
+#undef SKT_PICK_BN
+#undef SKT_GO
 }

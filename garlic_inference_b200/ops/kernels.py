@@ -294,7 +294,7 @@ def _streamk_workspace(device):
 
 
 def gemm_streamk_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
-    """x [M<=16, K] . w[N,K]^T on tcgen05 with W cut evenly over the SMs (TMA-fed, operands swapped: the rows of
+    """x [M<=64, K] . w[N,K]^T on tcgen05 with W cut evenly over the SMs (TMA-fed, operands swapped: the rows of
     W fill the 128-row side of the instruction).  Calls on one device share a work space, so they must not
     overlap (they do not on one stream)."""
     l = require_gpu()

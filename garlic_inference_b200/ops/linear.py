@@ -4,8 +4,9 @@ Which product runs:
   * float32 weight: this package's own float32 FMA kernel (no tensor-core or
     reduced-precision mode); bfloat16 activations are widened first and the
     result narrowed again.
-  * bfloat16 weight of 256 MB and more (the head), 1 to 16 rows: this package's
-    stream-K tcgen05 kernel, which cuts the weight evenly over the SMs.
+  * bfloat16 weight of 256 MB and more (the head), 1 to 64 rows, and of 90 MB
+    and more (the feed-forward's) at 9 to 32 rows: this package's stream-K
+    tcgen05 kernel, which cuts the weight evenly over the SMs.
   * bfloat16 weight, 1 to 8 rows: this package's tensor-core kernel for
     decode batches, which reads the weight once (or, when `GEMV_MAX_ROWS`
     says so, the plain bandwidth kernel for one row).
@@ -43,7 +44,15 @@ FUSED_SWIGLU_MIN_ROWS = int(os.environ.get("GARLIC_B200_FUSED_SWIGLU_ROWS", "512
 # 27.8 against 22.8 us on 101 MB; so smaller weights stay with the skinny kernel.  0 switches it off.
 STREAMK_MIN_BYTES = int(os.environ.get("GARLIC_B200_STREAMK_MIN_BYTES", str(256 << 20)))
 
-STREAMK_MAX_ROWS = 16
+STREAMK_MAX_ROWS = 64
+# From 9 to 32 rows (where the skinny kernel no longer competes and the alternative is the library product) the
+# stream-K kernel takes smaller weights too: it starts its stream of W behind the kernel before it, which a
+# library kernel does not.  Measured inside a decode step with the feed-forward's two products (201 and 101 MB)
+# on it / with the head only / with all products: 16 sequences 4.43 / 4.63 / 4.79 ms, 32 sequences 5.39 / 5.43 /
+# 5.72 ms.  At 64 sequences the kernel alone is slower than the library on those two (40.6 against 38.5 and 29.8
+# against 22.4 us) and the step with them 7.65 against 7.56 ms, so from 33 rows on it keeps the head only.
+STREAMK_WIDE_MAX_ROWS = 32
+STREAMK_MIN_BYTES_WIDE = int(os.environ.get("GARLIC_B200_STREAMK_MIN_BYTES_WIDE", str(90 << 20)))
 # Up to how many rows of x the plain bandwidth kernel (a warp per row of W) takes a product: none by default.
 # Alone it is as fast as the others at one row (175 us on the 1.24 GB head against 181 skinny and 183 stream-K),
 # but it gains nothing from being launched early behind its predecessor: a whole step of one sequence takes
@@ -51,6 +60,10 @@ STREAMK_MAX_ROWS = 16
 # everywhere.  GARLIC_B200_GEMV_ROWS=1 (or this variable) switches it on; the microbenchmark times it beside the others.
 GEMV_MAX_ROWS = int(os.environ.get("GARLIC_B200_GEMV_ROWS", "0"))
 SKINNY_MAX_ROWS = 8        # up to here: the tensor-core kernel that streams W once (it takes 16; the library is faster from 9 on)
+
+
+def _streamk_min_bytes(m: int) -> int:
+    return STREAMK_MIN_BYTES_WIDE if SKINNY_MAX_ROWS < m <= STREAMK_WIDE_MAX_ROWS else STREAMK_MIN_BYTES
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
@@ -70,7 +83,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
     aligned = k % 8 == 0 and w.data_ptr() % 16 == 0 and x.data_ptr() % 16 == 0
     if m <= GEMV_MAX_ROWS and aligned:
         return kernels.gemv_bf16(x, w, out_dtype)
-    if m <= STREAMK_MAX_ROWS and aligned and 0 < STREAMK_MIN_BYTES <= w.numel() * 2:
+    if m <= STREAMK_MAX_ROWS and aligned and 0 < _streamk_min_bytes(m) <= w.numel() * 2:
         return kernels.gemm_streamk_bf16(x, w, out_dtype)
     if m <= SKINNY_MAX_ROWS and aligned:
         return kernels.gemm_skinny_bf16(x, w, out_dtype)

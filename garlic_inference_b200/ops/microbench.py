@@ -121,9 +121,9 @@ def time_linear() -> None:
     for shape, (n, k) in SHAPES.items():
         copies = 2 if shape == "lm_head" else max(3, int(500e6 // (n * k * 2)) + 1)
         ws = _weights(shape, copies)
-        for m in (1, 2, 4, 8, 16, 64):
+        for m in (1, 2, 4, 8, 16, 32, 64):
             x = torch.randn(m, k, device=DEV, dtype=torch.bfloat16)
-            ops = (["gemv"] if m <= 8 else []) + (["skinny", "streamk"] if m <= 16 else []) + ["cublas"]
+            ops = (["gemv"] if m <= 8 else []) + (["skinny"] if m <= 16 else []) + ["streamk", "cublas"]
             res = {op: graph_time([(lambda w=w, op=op: _linear(op, x, w)) for w in ws]) for op in ops}
             print(f"{shape:8s} M={m:3d}  " + "  ".join(f"{op}: {ms * 1e3:7.1f} us {n * k * 2 / ms / 1e6:5.0f} GB/s"
                                                         for op, ms in res.items()), flush=True)

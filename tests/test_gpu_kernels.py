@@ -181,7 +181,9 @@ def test_gemm_skinny_swiglu_bf16(m, inter, k, split, wide):
 
 
 @pytest.mark.parametrize("m,n,k", [(1, 128, 64), (8, 100, 1000), (5, 264, 4096), (16, 4096, 4096), (8, 24576, 512), (3, 777, 72),
-                                   (8, 4096, 12288), (2, 151936, 256), (13, 6144, 4096)])
+                                   (8, 4096, 12288), (2, 151936, 256), (13, 6144, 4096), (17, 264, 4096), (32, 4096, 4096),
+                                   (33, 777, 72), (64, 6144, 4096), (48, 24576, 512), (64, 19456, 1024), (20, 19456, 512),
+                                   (64, 4096, 12288)])
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
 def test_gemm_streamk_bf16(m, n, k, out_dtype):
     """The decode product that cuts W evenly over the SMs: tiles whose parts lie in several CTAs are summed in

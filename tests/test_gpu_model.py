@@ -207,6 +207,7 @@ def test_streamk_products_in_the_model(model_dirs, plain_cache, monkeypatch):
     import sys
     from garlic_inference_b200 import AutoModel
     monkeypatch.setattr(sys.modules["garlic_inference_b200.ops.linear"], "STREAMK_MIN_BYTES", 1)
+    monkeypatch.setattr(sys.modules["garlic_inference_b200.ops.linear"], "STREAMK_MIN_BYTES_WIDE", 1)
     reqs, want = plain_cache("D")
     model = AutoModel.from_pretrained(model_dirs("D"), device=0, dtype="bfloat16", max_tokens=2048, page_size=64)
     for steps in (tiny.trace_tail_by_one(reqs, tail=32), tiny.trace_batched(reqs, BATCHES, prompt_frac=0.5)):
