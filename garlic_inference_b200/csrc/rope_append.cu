@@ -18,6 +18,8 @@
 // padding: its q is still written, nothing goes to the cache.
 #include "common.cuh"
 
+#include <type_traits>
+
 #define ROPE_WARPS 4
 
 template <typename T>
@@ -95,6 +97,35 @@ __global__ void qk_norm_rope_append_kernel(
     }
 }
 
+// A lane's N consecutive elements as the widest words that divide them (16, 8 or 4 bytes): one or two
+// instructions instead of N.  The address must be aligned to that word (the entry point checks the bases).
+template <typename T, int N>
+struct RopeWords {
+    static constexpr int bytes = N * (int)sizeof(T);
+    static constexpr int W = bytes % 16 == 0 ? 16 : (bytes % 8 == 0 ? 8 : 4);
+    static_assert(bytes % 4 == 0, "an even number of elements");
+    typedef typename std::conditional<W == 16, uint4, typename std::conditional<W == 8, uint2, uint32_t>::type>::type word;
+    union Both { word w[bytes / W]; T e[N]; __device__ Both() {} };
+};
+template <typename T, int N>
+__device__ __forceinline__ void rope_load(T (&r)[N], const T* p) {
+    typedef RopeWords<T, N> R;
+    typename R::Both u;
+#pragma unroll
+    for (int i = 0; i < R::bytes / R::W; ++i) u.w[i] = reinterpret_cast<const typename R::word*>(p)[i];
+#pragma unroll
+    for (int i = 0; i < N; ++i) r[i] = u.e[i];
+}
+template <typename T, int N>
+__device__ __forceinline__ void rope_store(T* p, const T (&r)[N]) {
+    typedef RopeWords<T, N> R;
+    typename R::Both u;
+#pragma unroll
+    for (int i = 0; i < N; ++i) u.e[i] = r[i];
+#pragma unroll
+    for (int i = 0; i < R::bytes / R::W; ++i) reinterpret_cast<typename R::word*>(p)[i] = u.w[i];
+}
+
 // The same for heads whose size is a multiple of 64 (up to 256) with the whole head rotated: a lane
 // holds EPL = d/32 consecutive elements, so that loads and stores are contiguous over the warp and the
 // rotation partner of lane l (the element half a head away) sits in lane l ^ 16.  A warp takes
@@ -160,13 +191,7 @@ __global__ void qk_norm_rope_append_vec_kernel(
     T raw[ROPE_GROUP][EPL];
 #pragma unroll
     for (int g = 0; g < ROPE_GROUP; ++g)
-        if (h0 + g < heads_here) {
-#pragma unroll
-            for (int e = 0; e < EPL; e += 2) {       // EPL is even: two elements (4 or 8 bytes) at a time
-                raw[g][e] = src[(size_t)(h0 + g) * d + e];
-                raw[g][e + 1] = src[(size_t)(h0 + g) * d + e + 1];
-            }
-        }
+        if (h0 + g < heads_here) rope_load<T, EPL>(raw[g], src + (size_t)(h0 + g) * d);
 #pragma unroll
     for (int g = 0; g < ROPE_GROUP; ++g) {
         const int h = h0 + g;
@@ -182,8 +207,7 @@ __global__ void qk_norm_rope_append_vec_kernel(
             dst = (is_k ? k_dst : v_dst) + (size_t)kvh * page_size * d;
         }
         if (!is_q && !is_k) {                        // values: copy
-#pragma unroll
-            for (int e = 0; e < EPL; ++e) dst[e] = raw[g][e];
+            rope_store<T, EPL>(dst, raw[g]);
             continue;
         }
         float x[EPL];
@@ -197,12 +221,13 @@ __global__ void qk_norm_rope_append_vec_kernel(
             for (int e = 0; e < EPL; ++e) x[e] = x[e] * inv * load_w(w, w_dtype, lane * EPL + e);
         }
         if (!pos_ok) { if (lane == 0) atomicExch(status, 3); continue; }
+        T y[EPL];
 #pragma unroll
         for (int e = 0; e < EPL; ++e) {
             const float other = __shfl_xor_sync(0xffffffffu, x[e], 16);
-            const float y = lane < 16 ? x[e] * cs[e] - other * sn[e] : x[e] * cs[e] + other * sn[e];
-            dst[e] = from_f32<T>(y);
+            y[e] = from_f32<T>(lane < 16 ? x[e] * cs[e] - other * sn[e] : x[e] * cs[e] + other * sn[e]);
         }
+        rope_store<T, EPL>(dst, y);
     }
 }
 
@@ -226,7 +251,9 @@ extern "C" int gi_qk_norm_rope_append(
     GI_REQUIRE(blocks < 2147483647LL, "gi_qk_norm_rope_append: too many (token, head) pairs");
     const size_t smem = (size_t)ROPE_WARPS * d * sizeof(float);
     cudaStream_t s = (cudaStream_t)stream;
-    if (d % 64 == 0 && d <= 256 && rotary_dim == d) {
+    const bool aligned = ((uintptr_t)qkv % 16 == 0) && ((uintptr_t)q_out % 16 == 0) && ((uintptr_t)k_pool % 16 == 0) &&
+                         ((uintptr_t)v_pool % 16 == 0);
+    if (d % 64 == 0 && d <= 256 && rotary_dim == d && aligned) {
         const int group = n_tokens >= 256 ? 4 : 1;
         const long long vec_items = (long long)n_tokens * ((heads_here + group - 1) / group);
         const long long vec_blocks = (vec_items + ROPE_WARPS - 1) / ROPE_WARPS;
