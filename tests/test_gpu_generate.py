@@ -126,3 +126,16 @@ def test_smoke_entry():
     sys.path.insert(0, str(tiny.REPO))
     import __graft_entry__ as entry
     entry.smoke()
+
+
+def test_timeline_of_a_recorded_step(model_dirs):
+    """`python -m garlic_inference_b200.engine.timeline` on a tiny model: the second build (with marks in the
+    kernels) compiles, every kernel of the replayed step leaves both marks in launch order, and the repeating
+    layer is found."""
+    cmd = [sys.executable, "-m", "garlic_inference_b200.engine.timeline", "--config",
+           str(model_dirs("D") / "config.json"), "--layers", "5", "--batch", "3", "--cached", "70"]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=900, cwd=str(tiny.REPO))
+    assert r.returncode == 0, r.stderr[-3000:]
+    head = r.stdout.splitlines()[0]
+    assert "kernels" in head and "a layer is 9 kernels" in head, r.stdout[:2000]
+    assert "a layer:" in r.stdout
