@@ -112,6 +112,15 @@ static inline void gi_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, si
     cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);      // errors surface in gi_check_launch
 }
 
+// The hash behind every counter-based random number of this library (sampling draws, random weights): the
+// splitmix64 finaliser.  Integer arithmetic only, so host and device agree bit for bit.
+__host__ __device__ __forceinline__ unsigned long long gi_mix64(unsigned long long z) {
+    z += 0x9E3779B97F4A7C15ull;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return z ^ (z >> 31);
+}
+
 __device__ __forceinline__ float to_f32(float v) { return v; }
 __device__ __forceinline__ float to_f32(bf16 v) { return __bfloat162float(v); }
 

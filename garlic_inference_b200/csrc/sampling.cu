@@ -12,21 +12,20 @@
 #include "common.cuh"
 #include <math.h>
 
-__host__ __device__ __forceinline__ unsigned long long gi_mix64(unsigned long long z) {
-    z += 0x9E3779B97F4A7C15ull;
-    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
-    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
-    return z ^ (z >> 31);
+// Uniform strictly inside (0, 1) from the 23 high bits of a hash: (k + 0.5) / 2^23 with k < 2^23 is exact in
+// float32 (24 significant bits), so the largest value is 1 - 2^-24 and never 1.  (With 24 bits k + 0.5 would
+// round to even, reach 2^24 and give u = 1, whose Gumbel term is +infinity.)
+__host__ __device__ __forceinline__ float gi_uniform_from_hash(unsigned long long h) {
+    return ((float)(h >> 41) + 0.5f) * (1.0f / 8388608.0f);
 }
 
-// uniform in (0, 1) from the generator's 24 high bits
 __host__ __device__ __forceinline__ float gi_uniform(unsigned long long seed, unsigned long long stream,
                                                      unsigned long long counter, unsigned long long index) {
     unsigned long long h = gi_mix64(seed);
     h = gi_mix64(h ^ stream);
     h = gi_mix64(h ^ counter);
     h = gi_mix64(h ^ index);
-    return ((float)(h >> 40) + 0.5f) * (1.0f / 16777216.0f);
+    return gi_uniform_from_hash(h);
 }
 
 #define SM_THREADS 256
@@ -117,3 +116,6 @@ extern "C" int gi_sample(const float* logits, long long row_stride, int n_rows, 
 extern "C" float gi_sample_uniform(unsigned long long seed, long long stream, int counter, int index) {
     return gi_uniform(seed, (unsigned long long)stream, (unsigned long long)counter, (unsigned long long)index);
 }
+
+// The last step of the generator alone: the uniform a given 64-bit hash turns into (for tests of its two ends).
+extern "C" float gi_sample_uniform_from_hash(unsigned long long h) { return gi_uniform_from_hash(h); }

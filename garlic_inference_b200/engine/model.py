@@ -52,8 +52,11 @@ class _PartLoader:
     def __init__(self, spec: PartSpec, source, rt: Runtime, shared: dict):
         self.spec, self.source, self.rt, self.shared = spec, source, rt, shared
 
-    def dtype(self, local: str) -> torch.dtype:
-        return device_dtype(self.source.stored_dtype(self.spec.weights[local]), self.rt.dtype)
+    def dtype(self, *locals_: str) -> torch.dtype:
+        """The type in which the named tensor is kept on the device; for several names (tensors packed into
+        one) the widest of theirs, so that a tensor stored in 32 bits is never narrowed by its neighbours."""
+        kept = [device_dtype(self.source.stored_dtype(self.spec.weights[n]), self.rt.dtype) for n in locals_]
+        return torch.float32 if torch.float32 in kept else kept[0]
 
     def __call__(self, local: str, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         name = self.spec.weights[local]

@@ -123,6 +123,16 @@ def cast(src: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
     return out
 
 
+def random_normal(out: torch.Tensor, key: int, mean: float, std: float) -> torch.Tensor:
+    """Fill `out` (float32 or bfloat16, dense) with mean + std * z_i, z_i a standard normal variate that
+    depends on (key, i) alone; `weights/random_init.py` holds the same arithmetic for the host."""
+    l = require_gpu()
+    _dense(out, "out")
+    check(l.gi_random_normal(_ptr(out), code(out.dtype), out.numel(), key & 0xFFFFFFFFFFFFFFFF, float(mean),
+                             float(std), _stream()), l)
+    return out
+
+
 def qk_norm_rope_append(qkv: torch.Tensor, n_q: int, n_kv: int, head_dim: int,
                         q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,
                         cos: torch.Tensor, sin: torch.Tensor, rotary_dim: int,

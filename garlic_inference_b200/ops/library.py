@@ -51,6 +51,9 @@ _SIGNATURES = {
     "gi_sample": ([P, L, I, I, P, P, P, c_ulonglong, P, P, P, P], I),
     "gi_sample_chunks": ([I], I),
     "gi_sample_uniform": ([c_ulonglong, L, I, I], F),
+    "gi_sample_uniform_from_hash": ([c_ulonglong], F),
+    "gi_random_normal": ([P, I, L, c_ulonglong, F, F, P], I),
+    "gi_random_sum12": ([c_ulonglong, c_ulonglong], I),
 }
 
 

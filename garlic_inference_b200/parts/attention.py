@@ -46,7 +46,8 @@ class GQAAttention(Mixer):
         self.qk_norm = bool(params.get("qk_norm", False))
         self.eps = float(params.get("qk_norm_eps", 1e-6))
         q_rows, kv_rows = self.n_q * self.d, self.n_kv * self.d
-        self.w_qkv = torch.empty((q_rows + 2 * kv_rows, self.hidden), dtype=load.dtype("q_proj"), device=rt.device)
+        self.w_qkv = torch.empty((q_rows + 2 * kv_rows, self.hidden), dtype=load.dtype("q_proj", "k_proj", "v_proj"),
+                                 device=rt.device)
         load("q_proj", out=self.w_qkv[:q_rows])
         load("k_proj", out=self.w_qkv[q_rows:q_rows + kv_rows])
         load("v_proj", out=self.w_qkv[q_rows + kv_rows:])

@@ -24,7 +24,8 @@ class SwiGLUMLP(FeedForward):
     def __init__(self, params, load, rt):
         super().__init__(params, load, rt)
         self.hidden, self.inter = int(params["hidden_size"]), int(params["intermediate_size"])
-        self.w_gate_up = torch.empty((2 * self.inter, self.hidden), dtype=load.dtype("gate_proj"), device=rt.device)
+        self.w_gate_up = torch.empty((2 * self.inter, self.hidden), dtype=load.dtype("gate_proj", "up_proj"),
+                                     device=rt.device)
         load("gate_proj", out=self.w_gate_up[:self.inter])
         load("up_proj", out=self.w_gate_up[self.inter:])
         self.w_down = load("down_proj")

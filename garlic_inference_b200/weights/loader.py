@@ -4,8 +4,13 @@ A folder holds either `model.safetensors` or shards named by
 `model.safetensors.index.json["weight_map"]` (upstream: src/models/loader.h:212-231).
 Before anything is copied to the GPU the whole list of tensors the model
 wants is compared with what the folder has, and ONE error lists everything
-that is wrong: missing tensors, unexpected tensors, wrong shapes.  Upstream
-checks no shape and reports a missing tensor only when it is first read
+that is wrong: missing tensors, wrong shapes, wrong types, with the tensors
+the model does not use listed beside them.  Tensors the model does not use
+are no error by themselves (a tied model whose file still stores
+`lm_head.weight`, a stray buffer): they are listed once in a
+`SurplusTensorWarning` and left on the disk, as upstream leaves them
+(src/models/qwen3/qwen3.cpp:58 never reads a stored head).  Upstream checks no
+shape and reports a missing tensor only when it is first read
 (loader.h:60-62, 234, 249).
 
 Precision on the device (`device_dtype`): a tensor stored in bfloat16 or
@@ -16,6 +21,7 @@ tensor is widened to float32 (exactly).
 from __future__ import annotations
 
 import json
+import warnings
 from dataclasses import dataclass
 from pathlib import Path
 
@@ -26,6 +32,10 @@ from .safetensors_io import SafetensorsError, SafetensorsFile
 
 class WeightError(ValueError):
     """The folder's tensors do not fit the model; the message lists every mismatch."""
+
+
+class SurplusTensorWarning(UserWarning):
+    """The folder holds tensors that the model does not use; the message lists them."""
 
 
 @dataclass(frozen=True)
@@ -85,7 +95,13 @@ class Checkpoint:
                  if n in have and tuple(self.shape(n)) != tuple(w.shape)]
         not_float = [(n, self.stored_dtype(n)) for n, w in wanted.items()
                      if n in have and w.role != "index" and not self.stored_dtype(n).is_floating_point]
-        if not (missing or unexpected or wrong or not_float):
+        self.unexpected = unexpected
+        if not (missing or wrong or not_float):
+            if unexpected:
+                shown = ", ".join(f"{n} {list(self.shape(n))}" for n in unexpected[:20])
+                more = f" and {len(unexpected) - 20} more" if len(unexpected) > 20 else ""
+                warnings.warn(f"{self.model_dir}: {len(unexpected)} tensors are not used by the model and were "
+                              f"not loaded: {shown}{more}", SurplusTensorWarning, stacklevel=2)
             return
         lines = [f"{self.model_dir}: the tensors do not fit the model "
                  f"({len(missing)} missing, {len(unexpected)} unexpected, {len(wrong)} of wrong shape)"]

@@ -121,3 +121,32 @@ def write_safetensors(path, tensors: dict[str, torch.Tensor], metadata: dict | N
             t = t.detach().contiguous().cpu()
             if t.numel():
                 f.write(t.reshape(-1).view(torch.uint8).numpy().data)
+
+
+def write_safetensors_lazy(path, entries: dict, make, metadata: dict | None = None) -> None:
+    """The same file, with each tensor made when its turn to be written comes: `entries` maps a name to
+    (dtype, shape), `make(name)` returns that tensor.  Only one tensor is in memory at a time."""
+    header: dict = {}
+    if metadata:
+        header["__metadata__"] = {str(k): str(v) for k, v in metadata.items()}
+    offset = 0
+    for name, (dtype, shape) in entries.items():
+        if dtype not in _NAMES:
+            raise SafetensorsError(f"tensor '{name}' has dtype {dtype}, which cannot be written")
+        nbytes = int(np.prod(shape, dtype=np.int64)) * torch.empty(0, dtype=dtype).element_size() if len(shape) else \
+            torch.empty(0, dtype=dtype).element_size()
+        header[name] = {"dtype": _NAMES[dtype], "shape": [int(d) for d in shape],
+                        "data_offsets": [offset, offset + nbytes]}
+        offset += nbytes
+    blob = json.dumps(header, separators=(",", ":")).encode("utf-8")
+    blob += b" " * ((8 - len(blob) % 8) % 8)
+    with open(path, "wb") as f:
+        f.write(struct.pack("<Q", len(blob)))
+        f.write(blob)
+        for name, (dtype, shape) in entries.items():
+            t = make(name).detach().contiguous().cpu()
+            if t.dtype != dtype or tuple(t.shape) != tuple(shape):
+                raise SafetensorsError(f"tensor '{name}' was announced as {dtype} {list(shape)} and made as "
+                                       f"{t.dtype} {list(t.shape)}")
+            if t.numel():
+                f.write(t.reshape(-1).view(torch.uint8).numpy().data)

@@ -6,11 +6,17 @@ config.json and for safetensors files and its own arithmetic.
 
 It rests on the formulas of NikolayBlagoev/garlic-inference (each function
 cites the file and lines it restates).  That project's model code is C++/CUDA
-with no CPU path for the dense model, so it cannot be run where these tests
-are written; nothing here was compared with its output.
+with no CPU path for the dense model, so it cannot run on the CPU.  It was
+compiled unmodified for a B200 with a small driver and run there on two tiny
+tied random models in bfloat16 (batch 2, prompts of 40 tokens, 8 decode steps);
+its logits are kept under tests/golden with the script that made them, and
+tests/test_reference_golden.py compares this file with them at every position:
+worst difference 3.4e-3 and 7.0e-3 of the largest logit (bfloat16 rounding),
+against 2e-1 to 1.3 for a wrong key/value head mapping or rotation.
 
 Two things are stated here that the upstream files leave to a library:
-  * grouped-query attention: query head h reads key/value head h // (n_q // n_kv);
+  * grouped-query attention: query head h reads key/value head h // (n_q // n_kv)
+    (confirmed by the comparison above);
   * a sliding window of w keys: query at position i sees keys j with
     i - w < j <= i (upstream has no window; w = None means every earlier key).
 """

@@ -532,6 +532,58 @@ def test_temperature_draws_follow_the_softmax_and_the_key():
     assert mixed[:10].tolist() == [int(row.argmax())] * 10 and torch.equal(mixed[10:], draws[10:])
 
 
+def test_a_token_that_cannot_be_drawn_is_never_drawn_at_a_real_vocabulary():
+    """A uniform of exactly 1 would give an infinite Gumbel term and let any entry win whatever its logit
+    (one in 2^24 per entry with a 24-bit uniform: about 1 % of the draws at 151,936 entries).  Every entry
+    but five is at -1e30 here; over 4,096 rows of the full vocabulary none of them may be drawn."""
+    vocab, n = 151936, 4096
+    logits = torch.full((n, vocab), -1e30, device=DEV)
+    allowed = torch.tensor([3, 70000, 100001, 151000, 151935], device=DEV)
+    logits[:, allowed] = torch.tensor([0.0, 0.3, -0.2, 0.1, 0.0], device=DEV)
+    temps = torch.full((n,), 1.5, device=DEV)
+    streams = torch.arange(n, dtype=torch.int64, device=DEV)
+    for counter in range(3):
+        counters = torch.full((n,), counter, dtype=torch.int32, device=DEV)
+        draws = K().sample(logits, temps, streams, counters, 77)
+        assert bool(torch.isin(draws.long(), allowed).all()), "a token at -1e30 was drawn"
+    freq = torch.bincount(draws.long(), minlength=vocab)[allowed].float().cpu() / n
+    p = torch.softmax(torch.tensor([0.0, 0.3, -0.2, 0.1, 0.0]) / 1.5, 0)
+    assert float((freq - p).abs().max()) < 4 * math.sqrt(0.25 / n)
+
+
+# ------------------------------------------------------------------ random weights
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_random_normal_kernel_gives_the_host_generator_s_bits(dtype):
+    from garlic_inference_b200.weights.random_init import normal_values, tensor_key
+    for name, n, mean, std in [("model.embed_tokens.weight", 100003, 0.0, 0.02), ("model.norm.weight", 96, 1.0, 0.2),
+                               ("x", 1, 0.0, 1.0), ("model.layers.3.mlp.up_proj.weight", 1 << 20, 0.0, 0.05)]:
+        key = tensor_key(11, name)
+        got = K().random_normal(torch.empty(n, dtype=dtype, device=DEV), key, mean, std).cpu()
+        want = torch.from_numpy(normal_values(key, n, mean, std)).to(dtype)
+        assert torch.equal(got, want), (name, dtype)
+    big = K().random_normal(torch.empty(1 << 22, dtype=torch.float32, device=DEV), 5, 0.0, 1.0)
+    assert abs(float(big.mean())) < 3e-3 and abs(float(big.std()) - 1.0) < 3e-3
+
+
+def test_a_folder_written_on_the_cpu_and_a_model_made_on_the_gpu_hold_the_same_tensors(tmp_path):
+    import tiny
+    from garlic_inference_b200 import AutoModel, write_random_model
+    from garlic_inference_b200.weights import Checkpoint
+    cfg = tiny.make_config("B")
+    folder = write_random_model(tmp_path / "m", cfg, seed=21, std=0.05, norm_std=0.2)
+    on_gpu = write_random_model(tmp_path / "g", cfg, seed=21, std=0.05, norm_std=0.2, device="cuda")
+    assert (folder / "model.safetensors").read_bytes() == (on_gpu / "model.safetensors").read_bytes()
+    model = AutoModel.from_random(cfg, seed=21, device=0, dtype="bfloat16", std=0.05, norm_std=0.2, max_tokens=256,
+                                  page_size=16)
+    ck = Checkpoint(folder)
+    mixer = model.model.blocks[2].mixer
+    q_rows = mixer.n_q * mixer.d
+    assert torch.equal(mixer.w_qkv[:q_rows].cpu(), ck.tensor("model.layers.2.self_attn.q_proj.weight"))
+    assert torch.equal(mixer.w_o.cpu(), ck.tensor("model.layers.2.self_attn.o_proj.weight"))
+    assert torch.equal(mixer.k_norm.cpu(), ck.tensor("model.layers.2.self_attn.k_norm.weight"))
+    assert torch.equal(model.model.head.weight.cpu(), ck.tensor("lm_head.weight"))
+
+
 # ------------------------------------------------------------------ tensor-core attention (bfloat16)
 def _tiles_for(runs):
     """runs: (slot, first row, rows, first position) per sequence -> int32 [n, 4] cut at 64 rows."""

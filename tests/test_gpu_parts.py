@@ -24,8 +24,9 @@ class DictLoader:
         from garlic_inference_b200.weights import device_dtype
         self.t, self.rt, self._dd = tensors, rt, device_dtype
 
-    def dtype(self, local):
-        return self._dd(self.t[local].dtype, self.rt.dtype)
+    def dtype(self, *locals_):
+        kept = [self._dd(self.t[n].dtype, self.rt.dtype) for n in locals_]
+        return torch.float32 if torch.float32 in kept else kept[0]
 
     def __call__(self, local, out=None):
         if out is not None:

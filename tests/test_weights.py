@@ -137,3 +137,83 @@ def test_device_dtype_policy():
     assert device_dtype(bf, f32) == f32 and device_dtype(f32, f32) == f32
     with pytest.raises(ValueError):
         device_dtype(bf, f16)
+
+
+def test_surplus_tensors_are_listed_in_a_warning_not_refused(tmp_path):
+    """A tied model whose file also stores lm_head.weight (and a stray buffer) loads; both are named once."""
+    from garlic_inference_b200.weights import SurplusTensorWarning
+    cfg = tiny.make_config("A")                                      # tied head
+    d = write_random_model(tmp_path / "m", cfg, seed=0)
+    ck = Checkpoint(d)
+    tensors = {n: ck.tensor(n).clone() for n in ck.names()}
+    tensors["lm_head.weight"] = tensors["model.embed_tokens.weight"].clone()
+    tensors["model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.ones(8)
+    write_safetensors(d / "model.safetensors", tensors)
+    with pytest.warns(SurplusTensorWarning) as rec:
+        ck2 = Checkpoint(d)
+        ck2.check(wanted_tensors(cfg.plan()))
+    assert len(rec) == 1
+    msg = str(rec[0].message)
+    assert "2 tensors are not used" in msg and "lm_head.weight [512, 64]" in msg and "inv_freq" in msg
+    assert ck2.unexpected == ["lm_head.weight", "model.layers.0.self_attn.rotary_emb.inv_freq"]
+
+
+def test_packed_tensors_keep_the_widest_stored_type(tmp_path):
+    """q in bfloat16, k and v in float32: the packed q/k/v weight is float32 and holds k and v exactly."""
+    from garlic_inference_b200.engine.model import DecoderModel
+    from garlic_inference_b200.parts import Runtime
+    cfg = tiny.make_config("A")
+    d = write_random_model(tmp_path / "m", cfg, seed=0)
+    ck = Checkpoint(d)
+    tensors = {n: ck.tensor(n).clone() for n in ck.names()}
+    g = torch.Generator().manual_seed(1)
+    k32 = torch.randn(tensors["model.layers.0.self_attn.k_proj.weight"].shape, generator=g) * 0.02
+    tensors["model.layers.0.self_attn.k_proj.weight"] = k32
+    tensors["model.layers.0.self_attn.v_proj.weight"] = tensors["model.layers.0.self_attn.v_proj.weight"].float()
+    tensors["model.layers.1.mlp.up_proj.weight"] = tensors["model.layers.1.mlp.up_proj.weight"].float() + 1e-4
+    write_safetensors(d / "model.safetensors", tensors)
+    ck = Checkpoint(d)
+    ck.check(wanted_tensors(cfg.plan()))
+    model = DecoderModel(cfg.plan(), ck, Runtime(torch.bfloat16, torch.device("cpu")))
+    a0, a1 = model.blocks[0].mixer, model.blocks[1].mixer
+    assert a0.w_qkv.dtype == torch.float32 and a1.w_qkv.dtype == torch.bfloat16
+    q_rows, kv_rows = a0.n_q * a0.d, a0.n_kv * a0.d
+    assert torch.equal(a0.w_qkv[q_rows:q_rows + kv_rows], k32)                 # not rounded to bfloat16
+    assert torch.equal(a0.w_qkv[:q_rows], tensors["model.layers.0.self_attn.q_proj.weight"].float())
+    assert model.blocks[1].feed_forward.w_gate_up.dtype == torch.float32
+    assert model.blocks[0].feed_forward.w_gate_up.dtype == torch.bfloat16
+
+
+def test_random_values_depend_on_seed_name_and_index_only():
+    from garlic_inference_b200.weights.random_init import normal_values, tensor_key
+    k = tensor_key(3, "model.layers.0.mlp.up_proj.weight")
+    assert k == tensor_key(3, "model.layers.0.mlp.up_proj.weight")
+    assert k != tensor_key(4, "model.layers.0.mlp.up_proj.weight") and k != tensor_key(3, "model.norm.weight")
+    whole = normal_values(k, 10000, 0.0, 1.0)
+    assert whole.dtype.name == "float32"
+    # any slice of the stream is the same numbers: the generator has no state
+    part = normal_values(k, 100, 0.0, 1.0, start=5000)
+    assert (part == whole[5000:5100]).all()
+    big = normal_values(k, 1 << 20, 0.0, 1.0)
+    assert abs(float(big.mean())) < 5e-3 and abs(float(big.std()) - 1.0) < 5e-3
+    assert float(abs(big).max()) <= 6.0
+    frac = float((abs(big) < 1.0).mean())
+    assert abs(frac - 0.6827) < 5e-3                       # a normal variate's one-sigma mass
+    shifted = normal_values(k, 1000, 1.0, 0.1)
+    assert ((shifted - 1.0) / 0.1 - whole[:1000]).__abs__().max() < 1e-5
+
+
+def test_the_compiled_generator_agrees_with_the_host_one():
+    """The integer part of the weight generator and the two ends of the sampling uniform, through the C ABI."""
+    from garlic_inference_b200.ops import ExtensionError, lib
+    from garlic_inference_b200.weights.random_init import normal_values
+    try:
+        l = lib()
+    except ExtensionError as e:                              # no nvcc on this machine
+        pytest.skip(str(e))
+    z = normal_values(987654321, 64, 0.0, 1.0)
+    for i in range(64):
+        assert (2 * l.gi_random_sum12(987654321, i) - 786420) / 131072 == float(z[i]), i
+    lo, hi = l.gi_sample_uniform_from_hash(0), l.gi_sample_uniform_from_hash(2 ** 64 - 1)
+    assert 0.0 < lo < 1e-6 and 1.0 - 1e-6 < hi < 1.0        # strictly inside (0, 1): no infinite Gumbel term
+    assert l.gi_sample_uniform_from_hash((2 ** 23 - 1) << 41) == hi

@@ -46,6 +46,12 @@ TINY = {
                        max_position_embeddings=1024, tie_word_embeddings=True, sliding_window=100,
                        layer_types=["sliding_attention", "full_attention", "sliding_attention"]),
               seed=4, std=0.05, norm_std=0.1),
+    # tied head, heads of 128 with four query heads per key/value head and n_heads * head_dim != hidden: what
+    # upstream's own code (always tied, bfloat16) can run too; tests/golden holds its logits for A and for this
+    "G": dict(cfg=dict(hidden_size=256, num_hidden_layers=2, num_attention_heads=8, num_key_value_heads=2,
+                       head_dim=128, intermediate_size=384, vocab_size=640, rope_theta=1e6, rms_norm_eps=1e-6,
+                       max_position_embeddings=512, tie_word_embeddings=True),
+              seed=5, std=0.04, norm_std=0.1),
 }
 
 # tolerances (never widened to pass): float32 logits against the plain float32 implementation,
