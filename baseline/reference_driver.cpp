@@ -40,6 +40,22 @@
 
 _TIMING_RESULTS tmrs{};       // upstream's timing macros add into this global (src/profiler.h:43)
 
+// Upstream allocates its activations anew in every forward pass and never checks an allocation
+// (src/models/qwen3/qwen3.cpp:263-288, src/tensor.h:66-70); whether and when its stream-ordered frees give the
+// memory back is the driver's business.  So before every pass this program checks that plenty is free and
+// stops with a message otherwise, instead of letting a kernel write through a null pointer.
+static double free_gb() {
+    size_t f = 0, t = 0;
+    cudaMemGetInfo(&f, &t);
+    return (double)f / 1e9;
+}
+static void need_free(double gb, const char* where) {
+    if (free_gb() < gb) {
+        fprintf(stderr, "reference_runner: only %.1f GB free before %s (%.1f wanted): stopping\n", free_gb(), where, gb);
+        exit(3);
+    }
+}
+
 static std::vector<KVCache> make_caches(const Qwen3Config& c, int pages, int batch, int pages_per_seq, cudaDataType_t t) {
     std::vector<KVCache> caches;
     caches.reserve(c.num_hidden_layers);
@@ -47,6 +63,15 @@ static std::vector<KVCache> make_caches(const Qwen3Config& c, int pages, int bat
         caches.emplace_back(c.num_key_value_heads, c.head_dim, pages, batch, pages_per_seq, t);
     for (auto& kv : caches) kv.prepare_table(pages_per_seq * PAGE_SIZE);     // map every page up front
     return caches;
+}
+
+// Upper bound of what one forward pass over B x S tokens allocates (bf16): the activations of
+// qwen3.cpp:263-288, four transposed copies per layer (qwen3.cpp:160-175), the logits, and as much again.
+static double pass_gb(const Qwen3Config& c, int B, int S) {
+    const double rows = (double)B * S, qd = (double)c.num_attention_heads * c.head_dim, kd = (double)c.num_key_value_heads * c.head_dim;
+    const double once = rows * (3.0 * c.hidden_size + 2 * qd + 2 * kd + 2.0 * c.intermediate_size + c.vocab_size + 4.0 * c.head_dim);
+    const double per_layer = rows * (2 * qd + 2 * kd + c.hidden_size);
+    return 2.0 * 2.0 * (once + c.num_hidden_layers * per_layer) / 1e9 + 2.0;
 }
 
 static void dump_logits(FILE* f, const Tensor& logits) {
@@ -110,6 +135,7 @@ int main(int argc, char** argv) {
         Tensor pos({B, S}, CUDA_R_32U);
         arrange(pos, 0, 1);
         cudaStreamSynchronize(get_compute_stream());
+        need_free(pass_gb(config, B, S), "a whole-prompt pass");
         cudaEventRecord(e0, get_compute_stream());
         for (auto& kv : caches) kv.prepare_table(S);
         Tensor logits = model->forward(x, pos, caches, engine);
@@ -131,12 +157,14 @@ int main(int argc, char** argv) {
         x.set_data<uint32_t>(xs, 4 * xs.size());
         Tensor pos({B, C}, CUDA_R_32U);
         arrange(pos, c0, 1);
+        need_free(pass_gb(config, B, C), "a prompt chunk");
         for (auto& kv : caches) kv.prepare_table(C);
         Tensor logits = model->forward(x, pos, caches, engine);
         if (dump) dump_logits(dump, logits);
         auto ret = argmax(logits, x);
         for (int b = 0; b < B; ++b) last[b] = ret[(size_t)b * C + C - 1];
     }
+    const double free_after_prompt = free_gb();
     Tensor x({B, 1}, CUDA_R_32U, 0);
     engine.get_graph(1, T);
     float dev_ms = 0;
@@ -153,6 +181,7 @@ int main(int argc, char** argv) {
         Tensor pos({B, 1}, CUDA_R_32U, 0);
         std::vector<uint32_t> p(B, (uint32_t)(S + j));
         pos.set_data<uint32_t>(p, 4 * (size_t)B);
+        if (j % 16 == 0) need_free(pass_gb(config, B, 1), "a decode step");
         for (auto& kv : caches) kv.prepare_table(1);
         Tensor logits = model->forward(x, pos, caches, engine);
         if (dump) dump_logits(dump, logits);
@@ -166,12 +195,14 @@ int main(int argc, char** argv) {
         wall_ms = std::chrono::duration<double, std::milli>(std::chrono::high_resolution_clock::now() - t0).count();
     }
     if (dump) fclose(dump);
+    const double free_at_end = free_gb();
     cudaError_t err = cudaDeviceSynchronize();
     printf("{\"batch\": %d, \"prompt_len\": %d, \"chunk\": %d, \"steps\": %d, \"warmup\": %d, \"layers\": %d, "
            "\"decode_ms_per_step\": %.6f, \"decode_wall_ms_per_step\": %.6f, \"h2d_bytes_per_step\": %lld, "
-           "\"d2h_bytes_per_step\": %d, \"last_token\": %u, \"cuda_error\": \"%s\", \"prefill_ms\": [",
+           "\"d2h_bytes_per_step\": %d, \"last_token\": %u, \"cuda_error\": \"%s\", \"free_gb_after_prompt\": %.2f, "
+           "\"free_gb_at_end\": %.2f, \"prefill_ms\": [",
            B, S, C, K, W, config.num_hidden_layers, K ? dev_ms / K : 0.0, K ? wall_ms / K : 0.0,
-           (long long)config.num_hidden_layers * B * pages_per_seq * 4 + 4LL * B, 4 * B, last[0], cudaGetErrorString(err));
+           (long long)config.num_hidden_layers * B * pages_per_seq * 4 + 4LL * B, 4 * B, last[0], cudaGetErrorString(err), free_after_prompt, free_at_end);
     for (size_t i = 0; i < prefill_ms.size(); ++i) printf("%s%.4f", i ? ", " : "", prefill_ms[i]);
     printf("]}\n");
     return err == cudaSuccess ? 0 : 1;

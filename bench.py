@@ -114,6 +114,138 @@ def prefill_flops(cfg, n_layers, tokens):
     return n_layers * (linear + attn) + 2 * vocab * h
 
 
+REFERENCE_RUNNER = os.path.join(ROOT, "baseline", "_ref", "bin", "reference_runner")
+
+
+def write_reference_model(folder, n_layers):
+    """An 8B-size folder for upstream's loader: the same tensors and shapes as the benchmark model, values
+    N(0, 0.02) drawn by torch on the GPU, norm weights 1, and `tie_word_embeddings` true because upstream
+    always uses the embedding table as the head (src/models/qwen3/qwen3.cpp:58): a decode step reads the same
+    bytes.  Nothing of this repository's compiled library is used."""
+    import torch
+    from garlic_inference_b200 import Qwen3Config
+    from garlic_inference_b200.engine.model import wanted_tensors
+    from garlic_inference_b200.weights.safetensors_io import write_safetensors_lazy
+    cfg = Qwen3Config(**{**QWEN3_8B, "num_hidden_layers": n_layers, "tie_word_embeddings": True})
+    wants = wanted_tensors(cfg.plan())
+    gen = torch.Generator(device="cuda").manual_seed(0)
+
+    def make(name):
+        w = wants[name]
+        if w.role == "norm":
+            return torch.ones(tuple(w.shape), dtype=torch.bfloat16)
+        t = torch.randn(tuple(w.shape), generator=gen, device="cuda", dtype=torch.bfloat16).mul_(0.02)
+        return t.cpu()
+
+    os.makedirs(folder, exist_ok=True)
+    with open(os.path.join(folder, "config.json"), "w") as f:
+        json.dump(cfg.to_dict(), f)
+    write_safetensors_lazy(os.path.join(folder, "model.safetensors"),
+                           {n: (torch.bfloat16, tuple(w.shape)) for n, w in wants.items()}, make)
+    torch.cuda.empty_cache()
+
+
+def reference_arm(args) -> int:
+    """Upstream's own dense Qwen3 code (built unmodified for sm_100a by baseline/build_reference.py, with the
+    driver baseline/reference_driver.cpp) on the benchmark's workload: the same JSON line, `impl: reference`."""
+    import shutil
+    import tempfile
+
+    def unavailable(why):
+        print(json.dumps({"impl": "reference", "unavailable": why}))
+        return 0
+
+    if not os.path.isfile(REFERENCE_RUNNER):
+        src = os.environ.get("GARLIC_REFERENCE_SRC", "/root/reference")
+        if not os.path.isdir(src):
+            return unavailable("baseline/_ref/bin/reference_runner is not built and there is no upstream checkout "
+                               "here to build it from (baseline/build_reference.py)")
+        r = subprocess.run([sys.executable, os.path.join(ROOT, "baseline", "build_reference.py"), "--src", src],
+                           capture_output=True, text=True)
+        if r.returncode != 0 or not os.path.isfile(REFERENCE_RUNNER):
+            return unavailable("building upstream's dense path failed: " + (r.stderr or r.stdout).strip()[-300:].replace("\n", " "))
+    import torch
+    if not torch.cuda.is_available():
+        return unavailable("no GPU here")
+    K, W = args.steps, max(args.warmup, 3)
+    n_layers = args.layers or QWEN3_8B["num_hidden_layers"]
+    pk = peaks()
+    props = torch.cuda.get_device_properties(0)
+    gpu_id = "GPU-" + str(props.uuid) if getattr(props, "uuid", None) else "0"
+    need = 2.2 * (n_layers * 385.9e6 + 1.25e9)                  # the file, with room to spare
+    base = next((d for d in ("/dev/shm", tempfile.gettempdir()) if os.path.isdir(d) and shutil.disk_usage(d).free > need), None)
+    if base is None:
+        return unavailable("no temporary folder with %.0f GB free for the model file" % (need / 1e9))
+    folder = tempfile.mkdtemp(prefix="garlic_ref_model_", dir=base)
+    try:
+        t0 = time.time()
+        write_reference_model(folder, n_layers)
+        print(f"bench.py: wrote the model folder in {time.time() - t0:.0f} s", file=sys.stderr, flush=True)
+
+        def run(batch, chunk, steps, warmup, repeats=0, clocks=None):
+            cmd = [REFERENCE_RUNNER, folder, "--batch", str(batch), "--prompt-len", str(CACHED), "--chunk", str(chunk),
+                   "--steps", str(steps), "--warmup", str(warmup), "--prefill-repeats", str(repeats)]
+            if clocks:
+                clocks.start()
+            r = subprocess.run(cmd, capture_output=True, text=True, timeout=1200)
+            if clocks:
+                clocks.stop()
+            if r.returncode != 0:
+                raise RuntimeError(f"reference_runner exited with {r.returncode}: {(r.stderr or r.stdout).strip()[-300:]}")
+            return json.loads(r.stdout.strip().splitlines()[-1])
+
+        clocks = ClockSampler(gpu_id)
+        try:
+            main_run = run(args.batch, 1024 if args.batch * CACHED * QWEN3_8B["vocab_size"] >= 2 ** 31 else CACHED, K, W,
+                           clocks=clocks)
+            pre = run(1, PREFILL_TOKENS, 0, 0, repeats=4)
+            points = {}
+            for b, chunk in (() if args.no_points else ((1, CACHED), (64, 128))):
+                try:                                   # a point that cannot run (memory) leaves the others standing
+                    points[f"decode_b{b}"] = b * 1e3 / run(b, chunk, K, W)["decode_ms_per_step"]
+                except RuntimeError as e:
+                    points[f"decode_b{b}_unavailable"] = str(e)[:200]
+        except (RuntimeError, subprocess.TimeoutExpired, ValueError, IndexError) as e:
+            return unavailable(str(e).replace("\n", " ")[:400])
+    finally:
+        shutil.rmtree(folder, ignore_errors=True)
+    ms = main_run["decode_ms_per_step"]
+    pre_ms = statistics.median(pre["prefill_ms"][1:])
+    total_b, weight_b, _ = decode_step_bytes(QWEN3_8B, n_layers, args.batch, CACHED + W + (K + 1) / 2)
+    achieved = total_b / (ms / 1e3) / 1e9
+    line = {
+        "impl": "reference",
+        "metric": f"decode tok/s at batch {args.batch} (Qwen3-8B layer sizes, {CACHED} cached tokens per sequence)",
+        "value": args.batch * 1e3 / ms, "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: random weights N(0, 0.02) in a model folder, token ids from a counter; the head is tied "
+                "because upstream always ties it (the same bytes are read per step)",
+        "config": {"model": "Qwen3-8B layer sizes", "global_batch": args.batch, "seq_len": CONTEXT,
+                   "cached_tokens": CACHED, "parallelism": "none (1 GPU)", "layers_run": n_layers,
+                   "layers_config": QWEN3_8B["num_hidden_layers"], "hidden_size": 4096, "n_heads": 32,
+                   "n_kv_heads": 8, "head_dim": 128, "intermediate_size": 12288, "vocab_size": 151936,
+                   "page_size": 32, "sampling": "upstream's argmax, result read by the host every step",
+                   "prompt_chunk": main_run["chunk"],
+                   "l2": "inputs exceed L2: a step reads %.1f GB of weights" % (weight_b / 1e9)},
+        "clocks": clocks.summary(),
+        # upstream's loop is synchronous: every step copies positions and block tables to the device and reads the
+        # argmax back, so the wall clock over the same steps is its end-to-end figure
+        "e2e": {"value": args.batch * 1e3 / main_run["decode_wall_ms_per_step"], "unit": "tokens/s",
+                "h2d_bytes_per_step": main_run["h2d_bytes_per_step"], "d2h_bytes_per_step": main_run["d2h_bytes_per_step"]},
+        "gpu_launches": 0,
+        "prefill": {"value": PREFILL_TOKENS / (pre_ms / 1e3), "tokens": PREFILL_TOKENS, "ms": pre_ms,
+                    "frac": (prefill_flops(QWEN3_8B, n_layers, PREFILL_TOKENS) + 2 * (PREFILL_TOKENS - 1) * 151936 * 4096)
+                    / (pre_ms / 1e3) / (pk["bf16_tflops"] * 1e12),
+                    "note": "upstream computes logits at all 2,048 positions and reads 2,048 argmax results back"},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": achieved / pk["hbm_gbs"], "bytes_per_step": total_b, "peaks": pk["source"]},
+        "points": points,
+        "memory": {"free_gb_after_prompt": main_run["free_gb_after_prompt"], "free_gb_at_end": main_run["free_gb_at_end"]},
+    }
+    print(json.dumps(line))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -127,11 +259,10 @@ def main() -> int:
     args = ap.parse_args()
 
     if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "NikolayBlagoev/garlic-inference is a CMake C++/CUDA program built for sm_120a only, with "
-                          "no setup.py or pyproject.toml (pip: 'not installable'), and its runner cannot run the "
-                          "dense model"}))
-        return 0
+        if args.gpus != 1:
+            print(json.dumps({"impl": "reference", "unavailable": "upstream runs on one GPU only"}))
+            return 0
+        return reference_arm(args)
     if args.gpus != 1:
         print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported (nothing was run)")
         return 2
