@@ -73,6 +73,94 @@ def test_every_cutting_agrees_with_the_plain_implementation(name, dtype, gpu_mod
                 assert np.array_equal(whole[rid][p], batched[rid][p]), f"{name}: {rid} position {p}: whole vs batched"
 
 
+def _large_batch_requests(name, n, seed):
+    """n + 8 requests of 50 to 110 tokens: a batch of n that starts together, then a batch of 8 in the same cache."""
+    vocab = tiny.TINY[name]["cfg"]["vocab_size"]
+    rng = np.random.default_rng(seed)
+    lengths = rng.integers(50, 111, size=n + 8).tolist()
+    reqs = tiny.random_requests(vocab, lengths, seed=seed + 1)
+    ids = list(reqs)
+    return reqs, [ids[:n], ids[n:]]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("n", [12, 20, 40, 70])
+@pytest.mark.parametrize("name", ["D", "E"])
+def test_batches_of_many_sequences(name, n, dtype, model_dirs):
+    """Batches of 12, 20, 40 and 70 sequences of unequal lengths that start together (unequal prompts in one step),
+    then decode for 40 to 80 steps while the shorter ones end, then a second batch in the slots and pages the first
+    gave back: the recorded steps of 16, 32, 64 and 128 rows with their padding rows, the products that take 9 to
+    64 rows and more, and the decode attention that writes its output itself (256 and more (sequence, head) pairs)."""
+    from garlic_inference_b200 import AutoModel
+    reqs, batches = _large_batch_requests(name, n, seed=1000 + n)
+    want = tiny.plain_logits(model_dirs(name), reqs)
+    max_tokens = sum(_round64(len(reqs[r])) for r in batches[0])
+    model = AutoModel.from_pretrained(model_dirs(name), device=0, dtype=dtype, max_tokens=max_tokens, page_size=64)
+    steps = tiny.trace_batched(reqs, batches, prompt_frac=0.25)
+    assert sum(1 for s in steps if len(s["entries"]) >= min(n, 9)) >= 12      # many steps at (nearly) full width
+    got = tiny.run_trace_in_process(model, steps)
+    tiny.assert_covers(got, reqs)
+    worst = tiny.compare(got, want, tiny.TOL[dtype], f"{name} {dtype} batch of {n}")
+    print(f"{name} {dtype} batch of {n}: worst relative error {worst:.3e}")
+    buckets = sorted(model.engine.graphs._graphs)
+    assert max(buckets) == 1 << (n - 1).bit_length(), buckets
+    cache = model.engine.cache
+    assert cache.slots.n_free == cache.max_slots
+    assert all(g.host.pool.n_free == g.host.pool.n_pages for g in cache.groups), "a page was lost"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_decode_batches_beyond_the_largest_recorded_size(dtype, model_dirs):
+    """With the largest recorded batch size forced down to 8, a batch of 12 decodes launch by launch and smaller
+    ones (as its sequences end) from recorded steps: both against the plain implementation."""
+    from garlic_inference_b200 import AutoModel
+    reqs, batches = _large_batch_requests("D", 12, seed=2012)
+    want = tiny.plain_logits(model_dirs("D"), reqs)
+    model = AutoModel.from_pretrained(model_dirs("D"), device=0, dtype=dtype, max_tokens=4096, page_size=64)
+    model.engine.graphs.largest = 8
+    got = tiny.run_trace_in_process(model, tiny.trace_batched(reqs, batches, prompt_frac=0.25))
+    tiny.assert_covers(got, reqs)
+    tiny.compare(got, want, tiny.TOL[dtype], f"D {dtype} batch of 12, recorded sizes up to 8")
+    assert max(model.engine.graphs._graphs) == 8
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["B", "D", "E"])
+def test_mixed_steps(name, dtype, gpu_models, model_dirs):
+    """Steps that mix: request x decodes one token a step while request y's prompt arrives in two chunks of 70 and
+    59 tokens, and request z's whole prompt arrives later beside both decoding."""
+    vocab = tiny.TINY[name]["cfg"]["vocab_size"]
+    reqs = tiny.random_requests(vocab, [90, 160, 75], seed=31)
+    x, y, z = reqs["r0"], reqs["r1"], reqs["r2"]
+    want = tiny.plain_logits(model_dirs(name), reqs)
+    model = gpu_models(name, dtype, max_tokens=4096, page_size=64 if name in "DE" else 16)
+    steps = [{"step": 0, "entries": [{"id": "r0", "tokens": x[:50], "want": list(range(50))}], "end": []},
+             {"step": 1, "entries": [{"id": "r0", "tokens": [x[50]], "want": [0]},
+                                     {"id": "r1", "tokens": y[:70], "want": list(range(70))}], "end": []},
+             {"step": 2, "entries": [{"id": "r1", "tokens": y[70:129], "want": list(range(59))},
+                                     {"id": "r0", "tokens": [x[51]], "want": [0]}], "end": []}]
+    nx, ny, nz = 52, 129, 0
+    while nx < len(x) or ny < len(y) or nz < len(z):
+        entries = []
+        if nx < len(x):
+            entries.append({"id": "r0", "tokens": [x[nx]], "want": [0]})
+            nx += 1
+        if ny < len(y):
+            entries.append({"id": "r1", "tokens": [y[ny]], "want": [0]})
+            ny += 1
+        if nz == 0 and nx >= 60:
+            entries.append({"id": "r2", "tokens": z[:40], "want": list(range(40))})      # a prompt beside decoding rows
+            nz = 40
+        elif 0 < nz < len(z):
+            entries.append({"id": "r2", "tokens": [z[nz]], "want": [0]})
+            nz += 1
+        steps.append({"step": len(steps), "entries": entries, "end": []})
+    steps[-1]["end"] = ["r0", "r1", "r2"]
+    got = tiny.run_trace_in_process(model, steps)
+    tiny.assert_covers(got, reqs)
+    tiny.compare(got, want, tiny.TOL[dtype], f"{name} {dtype} mixed steps")
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_float32_is_far_closer_than_bfloat16(dtype, gpu_models, plain_cache):
     """The float32 path is a true 32-bit path: its error is orders of magnitude below bfloat16's."""

@@ -53,3 +53,27 @@ def test_float32_at_production_sizes(big_layer):
     tail = tiny.run_trace_in_process(model, tiny.trace_tail_by_one(short, tail=8))
     assert tiny.compare(whole, want, tiny.TOL["float32"], "production-size layer, float32, whole") < 2e-5
     tiny.compare(tail, want, tiny.TOL["float32"], "production-size layer, float32, last 8 one by one")
+
+
+@pytest.mark.parametrize("n", [20, 40, 70])
+def test_batches_of_many_sequences_at_the_benchmark_s_layer_sizes(n, tmp_path_factory):
+    """One layer of the benchmark model's sizes, batches of 20, 40 and 70 sequences that start together with short
+    unequal prompts and decode 40 steps and more (recorded steps of 32, 64 and 128 rows), then a second batch in the
+    same cache: the products that take 9 to 32 rows (the feed-forward's go to the stream-K kernel there), 33 to 64
+    rows and more, at the shapes whose throughput the benchmark reports."""
+    import numpy as np
+    from garlic_inference_b200 import AutoModel, Qwen3Config, write_random_model
+    cfg = dict(COMMON, **SIZES["8B"])
+    folder = write_random_model(tmp_path_factory.mktemp("layer_8B_wide"), Qwen3Config(**cfg), seed=6, std=0.02, norm_std=0.1)
+    rng = np.random.default_rng(n)
+    lengths = rng.integers(48, 65, size=n + 4).tolist()
+    reqs = tiny.random_requests(cfg["vocab_size"], lengths, seed=n + 1)
+    ids = list(reqs)
+    want = tiny.plain_logits(folder, reqs)
+    model = AutoModel.from_pretrained(folder, device=0, dtype="bfloat16", max_tokens=64 * n, page_size=64)
+    steps = tiny.trace_batched(reqs, [ids[:n], ids[n:]], prompt_frac=0.12)
+    got = tiny.run_trace_in_process(model, steps)
+    tiny.assert_covers(got, reqs)
+    worst = tiny.compare(got, want, tiny.TOL["bfloat16"], f"8B-size layer, bfloat16, batch of {n}")
+    print(f"8B-size layer, batch of {n}: worst relative error {worst:.3e}")
+    assert max(model.engine.graphs._graphs) == 1 << (n - 1).bit_length()
