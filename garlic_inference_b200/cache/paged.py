@@ -116,7 +116,9 @@ class PagedCache:
             if isinstance(req, KVRequirement):
                 by_req.setdefault(req, []).append(e)
             elif isinstance(req, StateRequirement):
-                self._state_of_entry[e] = torch.zeros((self.max_slots, *req.shape), dtype=req.dtype,
+                # one row per slot and a spare last row: a padding row of a recorded step carries slot -1,
+                # which as an index is that spare, so it reads and writes nothing a sequence owns
+                self._state_of_entry[e] = torch.zeros((self.max_slots + 1, *req.shape), dtype=req.dtype,
                                                       device=self.device)
             elif req is not None:
                 raise CacheError(f"cache entry {e}: unknown requirement {req!r}")

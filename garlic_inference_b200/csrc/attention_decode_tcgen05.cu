@@ -464,12 +464,7 @@ extern "C" int gi_attention_decode_tcgen05(const void* q, const void* k_pool, co
     if (int rc = fd_make_map(&map_k, k_pool, pool_rows, d, FD_BN)) return rc;
     if (int rc = fd_make_map(&map_v, v_pool, pool_rows, d, FD_BN)) return rc;
     const size_t smem = (size_t)FD_Q_BYTES + 2 * FD_STAGES * FD_KV_BYTES + sizeof(FdControl) + 1024;
-    static bool attr_done = false;
-    if (!attr_done) {
-        cudaError_t e = cudaFuncSetAttribute((const void*)decode_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) { gi_set_error("gi_attention_decode_tcgen05: shared memory: %s", cudaGetErrorString(e)); return (int)e; }
-        attr_done = true;
-    }
+    if (int rc = gi_reserve_smem((const void*)decode_tcgen05_kernel, smem, "gi_attention_decode_tcgen05")) return rc;
     gi_launch(decode_tcgen05_kernel, dim3(n_splits, n_kv, n_seqs), dim3(FD_THREADS), smem, (cudaStream_t)stream, map_q, map_k,
               map_v, block_table, tok_pos, tok_slot, part_o, part_ml, (bf16*)out, n_q, n_kv, page_size, max_pages, n_pool_pages, window,
               scale * 1.4426950408889634f, n_splits, error_flag);

@@ -479,16 +479,9 @@ static int check_common(const char* who, int n_q, int n_kv, int d, int page_size
     return 0;
 }
 
-// Raises a kernel's dynamic shared memory limit, once per kernel (the attribute is kept by the runtime).
+// Raises a kernel's dynamic shared memory limit, once per kernel and device.
 template <int D, int WHICH>
-static int set_smem(const void* kernel, size_t bytes) {
-    static bool done = false;
-    if (done) return 0;
-    done = true;
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
-    if (e != cudaSuccess) { gi_set_error("attention: cannot reserve %zu bytes of shared memory: %s", bytes, cudaGetErrorString(e)); return (int)e; }
-    return 0;
-}
+static int set_smem(const void* kernel, size_t bytes) { return gi_reserve_smem(kernel, bytes, "attention"); }
 
 // tiles: int32 [n_tiles, 4] = {slot, first q row, rows (<= 64), position of the first row}
 extern "C" int gi_attention_prefill_bf16(const void* q, const void* k_pool, const void* v_pool, const int* block_table,

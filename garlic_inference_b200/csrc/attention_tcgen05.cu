@@ -497,12 +497,7 @@ extern "C" int gi_attention_prefill_tcgen05(const void* q, const void* k_pool, c
     if (int rc = ft_make_map(&map_k, k_pool, pool_rows, d, FT_BN)) return rc;
     if (int rc = ft_make_map(&map_v, v_pool, pool_rows, d, FT_BN)) return rc;
     const size_t smem = (size_t)FT_Q_BYTES + 2 * FT_STAGES * FT_KV_BYTES + sizeof(FtControl) + 1024;
-    static bool attr_done = false;
-    if (!attr_done) {
-        cudaError_t e = cudaFuncSetAttribute((const void*)flash_prefill_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) { gi_set_error("gi_attention_prefill_tcgen05: shared memory: %s", cudaGetErrorString(e)); return (int)e; }
-        attr_done = true;
-    }
+    if (int rc = gi_reserve_smem((const void*)flash_prefill_tcgen05_kernel, smem, "gi_attention_prefill_tcgen05")) return rc;
     int n_sm = 148;
     {
         int dev = 0;

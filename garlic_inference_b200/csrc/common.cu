@@ -51,3 +51,26 @@ extern "C" int gi_device_arch(void) {
     }
     return major * 10 + minor;
 }
+
+#include <mutex>
+#include <vector>
+namespace {
+struct SmemRecord { const void* kernel; int device; size_t bytes; };
+std::mutex g_smem_mutex;
+std::vector<SmemRecord> g_smem_done;
+}
+int gi_reserve_smem(const void* kernel, size_t bytes, const char* who) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) { gi_set_error("%s: %s", who, cudaGetErrorString(e)); return (int)e; }
+    std::lock_guard<std::mutex> lock(g_smem_mutex);
+    for (const SmemRecord& r : g_smem_done)
+        if (r.kernel == kernel && r.device == dev && r.bytes >= bytes) return 0;
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (e != cudaSuccess) {
+        gi_set_error("%s: cannot reserve %zu bytes of shared memory: %s", who, bytes, cudaGetErrorString(e));
+        return (int)e;
+    }
+    g_smem_done.push_back({kernel, dev, bytes});
+    return 0;
+}

@@ -26,6 +26,9 @@ const char* gi_last_error(void);
 
 void gi_set_error(const char* fmt, ...);
 int gi_check_launch(const char* what);
+// Raises `kernel`'s limit of dynamic shared memory to `bytes` on the current device; remembered per kernel and
+// device only once it has succeeded, so a second device, or a call after a failed one, sets it again.
+int gi_reserve_smem(const void* kernel, size_t bytes, const char* who);
 
 #define GI_REQUIRE(cond, ...)                 \
     do {                                      \

@@ -224,13 +224,7 @@ static int launch_skinny(const bf16* x, const bf16* W, void* out, int out_f32, i
                          cudaStream_t stream) {
     constexpr int MP = 8 * NT, R = 16 * WR, KC = 64 * WK;
     const size_t smem = (size_t)SK_DEPTH * 4 * SK_THREADS * 16 + (size_t)(WK + 1) * MP * R * sizeof(float);
-    static bool attr_done = false;
-    if (!attr_done) {
-        cudaError_t e = cudaFuncSetAttribute((const void*)skinny_gemm_kernel<NT, WR, WK, GLU>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) { gi_set_error("gi_gemm_skinny_bf16: shared memory: %s", cudaGetErrorString(e)); return (int)e; }
-        attr_done = true;
-    }
+    if (int rc = gi_reserve_smem((const void*)skinny_gemm_kernel<NT, WR, WK, GLU>, smem, "gi_gemm_skinny_bf16")) return rc;
     const int k_slice = ((K + n_split - 1) / n_split + KC - 1) / KC * KC;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(GLU ? (N / 2 + R / 2 - 1) / (R / 2) : (N + R - 1) / R, n_split, 1);

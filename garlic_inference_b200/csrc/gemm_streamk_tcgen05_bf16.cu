@@ -129,7 +129,7 @@ template <int OUT_F32, int SKT_STAGES, int BN>
 __global__ void __launch_bounds__(SKT_THREADS, 1)
 gemm_streamk_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                             void* __restrict__ out, float* __restrict__ partials, int* __restrict__ flags,
-                            int M, int N, int K, int* __restrict__ error_flag) {
+                            int M, int N, int K, int* __restrict__ error_flag, int unanswered_limit) {
     constexpr int SKT_X_BYTES = BN * SKT_BK * 2;
     constexpr int SKT_TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;       // two accumulators of BN columns
     gi_pdl_launch_dependents();
@@ -284,7 +284,9 @@ gemm_streamk_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __g
                 for (int m = 0; m < BN; ++m) slot[m * SKT_ROWS + row_in_tile] = v[m];
                 __threadfence();
                 skt_epilogue_any(false);
-                if (threadIdx.x == 64) asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(flags + c), "r"(1) : "memory");
+                // (unanswered_limit > 0 is the test of the wait below: the flag is held back, so the wait must run out)
+                if (threadIdx.x == 64 && unanswered_limit == 0)
+                    asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(flags + c), "r"(1) : "memory");
             } else {
                 if (sg.kb < kb_per_tile) {
                     // the head of a tile: the CTAs after this one hold the rest, each as the first thing it did
@@ -297,9 +299,10 @@ gemm_streamk_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __g
                         cov = e2 < tile_end ? e2 : tile_end;
                     }
                     int missing = 0;
+                    const int spin_limit = unanswered_limit > 0 ? unanswered_limit : SKT_SPIN_LIMIT;
                     for (int j = (int)(threadIdx.x - 64); j < n_after; j += 128) {
                         int seen = 0;
-                        for (int i = 0; i < SKT_SPIN_LIMIT && !seen; ++i) {
+                        for (int i = 0; i < spin_limit && !seen; ++i) {
                             asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(flags + c + 1 + j) : "memory");
                             if (!seen && (i & 255) == 255 && *abort) break;
                         }
@@ -391,24 +394,28 @@ static bool gi_streamk_whole_tiles_enabled() {
 }
 
 // Floats of work space and ints of flags the entry point below wants (for any shape): one slot and one flag
-// per CTA.  The flags must be zero before the first call; every call leaves them zero.
+// per CTA.  The flags must be zero before the first call; every call that ends without an error leaves them
+// zero.  After a call that recorded an error (a wait that ran out) the flags are undefined: CTAs that had
+// announced their partial sums were never answered.  Zero them before the next call.
 extern "C" long long gi_gemm_streamk_workspace_floats(void) { return (long long)SKT_MAX_CTAS * SKT_SLOT_FLOATS; }
 extern "C" int gi_gemm_streamk_flags(void) { return SKT_MAX_CTAS; }
+
+// For the test of the bounded wait: with a limit above zero the CTAs that hold the tail of a cut tile write their
+// partial sums but hold back the flag that announces them, and the CTA that holds the tile's head waits at most
+// `limit` polls for it.  The wait runs out, the CTA records code 34 in *error_flag, skips its tile and returns;
+// nothing else of the kernel changes, no copy or product is in flight for the waiting warps, and the flags stay
+// zero.  0 (the default) is the product as it is used.
+static int g_skt_unanswered_limit = 0;
+extern "C" void gi_gemm_streamk_test_unanswered_flags(int limit) { g_skt_unanswered_limit = limit > 0 ? limit : 0; }
 
 template <int OUT_F32, bool WHOLE, int BN>
 static int skt_launch(const CUtensorMap& map_w, const CUtensorMap& map_x, void* out, float* partials, int* flags, int M, int N,
                       int K, long long g, int* error_flag, cudaStream_t stream) {
     constexpr int stages = skt_stages(BN, WHOLE);
     const size_t smem = (size_t)stages * (SKT_W_BYTES + BN * SKT_BK * 2) + sizeof(SktControl) + 1024;
-    static bool attr_done = false;
-    if (!attr_done) {
-        cudaError_t e = cudaFuncSetAttribute((const void*)gemm_streamk_tcgen05_kernel<OUT_F32, stages, BN>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) { gi_set_error("gi_gemm_streamk_bf16: shared memory: %s", cudaGetErrorString(e)); return (int)e; }
-        attr_done = true;
-    }
+    if (int rc = gi_reserve_smem((const void*)gemm_streamk_tcgen05_kernel<OUT_F32, stages, BN>, smem, "gi_gemm_streamk_bf16")) return rc;
     gi_launch(gemm_streamk_tcgen05_kernel<OUT_F32, stages, BN>, dim3((unsigned)g), dim3(SKT_THREADS), smem, stream, map_w, map_x,
-              out, partials, flags, M, N, K, error_flag);
+              out, partials, flags, M, N, K, error_flag, g_skt_unanswered_limit);
     return gi_check_launch("gi_gemm_streamk_bf16");
 }
 

@@ -116,6 +116,16 @@ class DecoderModel:
             written[e.cache] = written[e.cache] or e.writes_cache
         return reqs
 
+    def step_arrays(self, shape, cache) -> dict:
+        """The int32 arrays the scheduled layers' parts want on the device for this step, each name made once
+        ({name: numpy array}); the engine copies them with the step's own arrays."""
+        out: dict = {}
+        for e in self.schedule:
+            for name, make in self.blocks[e.layer].step_arrays(shape, cache.view(e.cache)).items():
+                if name not in out:
+                    out[name] = make()
+        return out
+
     def forward(self, ctx: StepContext, cache, want_rows: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
         """Run the step's tokens through every scheduled layer; float32 logits [n_wanted, vocab] at
         `want_rows` (int32 row indices), or None when nothing is wanted."""

@@ -20,7 +20,7 @@ import numpy as np
 import torch
 
 from ..cache import PagedCache
-from ..parts import StepContext
+from ..parts import StepContext, StepShape
 from .model import DecoderModel
 
 
@@ -46,7 +46,11 @@ class _Staging:
         self.bytes_uploaded = 0
 
     def upload(self, arrays: list[np.ndarray]) -> list[torch.Tensor]:
-        total = sum(a.size for a in arrays)
+        """Copy the int32 arrays to the device in one transfer; each starts on a 16-byte boundary."""
+        offsets, total = [], 0
+        for a in arrays:
+            offsets.append(total)
+            total += -(-a.size // 4) * 4
         if total > self.capacity:
             self.capacity = max(1024, 2 * total)
             self.host = torch.empty(self.capacity, dtype=torch.int32)
@@ -56,12 +60,11 @@ class _Staging:
             self.event = None
         if self.event is not None:
             self.event.synchronize()                 # the last copy out of the pinned buffer is done
-        out, off = [], 0
+        out = []
         host_np = self.host.numpy()
-        for a in arrays:
+        for a, off in zip(arrays, offsets):
             host_np[off:off + a.size] = a
             out.append(self.dev[off:off + a.size])
-            off += a.size
         self.dev[:total].copy_(self.host[:total], non_blocking=True)
         self.bytes_uploaded += 4 * total
         if self.device.type == "cuda":
@@ -149,27 +152,15 @@ class Engine:
                 if want_rows.size == len(slots):         # one token each and each wanted: rows as they are
                     return logits
                 return logits[torch.from_numpy(want_rows.astype(np.int64)).to(logits.device)]
-        single = all(n == 1 for n in lens)
-
-        def runs(rows: int) -> np.ndarray:
-            if single:
-                return np.zeros((0, 4), dtype=np.int32)
-            tiles = [(s, st + r0, min(rows, n - r0), p + r0)
-                     for s, st, n, p in zip(slots, starts, lens, past) for r0 in range(0, n, rows)]
-            # the runs with the most keys to walk go first, so that the last CTAs to start are short ones
-            tiles.sort(key=lambda t: -(t[3] + t[2]))
-            return np.asarray(tiles, dtype=np.int32)
-
-        tiles, tiles128 = runs(64), runs(128)
-        # the runs go first: the kernels read them 16 bytes at a time
-        d_tiles, d_tiles128, d_toks, d_pos, d_slot, d_want = self._staging.upload(
-            [tiles.reshape(-1), tiles128.reshape(-1), toks, pos, slot, want_rows])
+        shape = StepShape(slots, starts, lens, past, all(n == 1 for n in lens))
+        extra = self.model.step_arrays(shape, self.cache)          # what the parts want on the device besides
+        uploaded = self._staging.upload([*(a.reshape(-1) for a in extra.values()), toks, pos, slot, want_rows])
+        n_extra = len(extra)
+        d_toks, d_pos, d_slot, d_want = uploaded[n_extra:]
         ctx = StepContext(
             n_tokens=int(toks.size), tokens=d_toks, tok_pos=d_pos, tok_slot=d_slot,
-            q_tiles=None if single else d_tiles.view(-1, 4),
-            q_tiles128=None if single else d_tiles128.view(-1, 4),
-            seq_slots=slots, seq_starts=starts, seq_lens=lens, seq_past=past,
-            all_single=all(n == 1 for n in lens),
+            arrays={name: dev.view(a.shape) for (name, a), dev in zip(extra.items(), uploaded[:n_extra])},
+            seq_slots=slots, seq_starts=starts, seq_lens=lens, seq_past=past, all_single=shape.all_single,
             max_kv_len=max(p + n for p, n in zip(past, lens)),
             status=self.cache.status)
         logits = self.model.forward(ctx, self.cache, d_want if want_rows.size else None)
@@ -231,9 +222,4 @@ class Engine:
         self.cache.check_status()
         if self.rt.device.type == "cuda":
             from ..ops import kernels
-            flag = kernels.tcgen05_error_flag(self.rt.device)
-            code = int(flag.item())
-            if code:
-                flag.zero_()
-                raise RuntimeError(f"a tcgen05 kernel gave up a bounded wait (code {code}: 11-13 product, "
-                                   "21-23 attention, 24 unmapped page)")
+            kernels.check_bounded_waits(self.rt.device)

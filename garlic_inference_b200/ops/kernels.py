@@ -276,6 +276,31 @@ def tcgen05_error_flag(device) -> torch.Tensor:
     return _tcgen05_flag[key]
 
 
+class WaitRanOut(RuntimeError):
+    """A kernel gave up one of its bounded waits; what it was writing is unspecified."""
+
+
+def check_bounded_waits(device) -> None:
+    """Raise `WaitRanOut` if a tcgen05 kernel launched on `device` since the last check gave up a bounded wait
+    (synchronises).  The flag is cleared and the stream-K product's hand-over flags are zeroed, since a kernel
+    that gave up may have left some of them set: the next call starts clean."""
+    flag = tcgen05_error_flag(device)
+    code = int(flag.item())
+    if code:
+        flag.zero_()
+        key = torch.device(device).index or 0
+        if key in _streamk_space:
+            _streamk_space[key][1].zero_()
+        raise WaitRanOut(f"a tcgen05 kernel gave up a bounded wait (code {code}: 11-13 product, 21-23 attention, "
+                         "24 unmapped page, 31-33 stream-K product, 34 a partial sum that was never announced)")
+
+
+def streamk_test_unanswered_flags(limit: int) -> None:
+    """For the test of the bounded wait: with `limit` > 0 the stream-K product's hand-over flags are held back
+    and the wait for them gives up after `limit` polls (see the kernel file); 0 restores the product."""
+    require_gpu().gi_gemm_streamk_test_unanswered_flags(int(limit))
+
+
 def gemm_tcgen05_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
     """x [M, K] . w[N, K]^T for many rows on tcgen05 tensor cores (TMA-fed, accumulators in tensor memory)."""
     l = require_gpu()

@@ -47,6 +47,7 @@ _SIGNATURES = {
     "gi_gemm_streamk_bf16": ([P, P, P, I, I, I, I, P, P, P, P], I),
     "gi_gemm_streamk_workspace_floats": ([], L),
     "gi_gemm_streamk_flags": ([], I),
+    "gi_gemm_streamk_test_unanswered_flags": ([I], None),
     "gi_gemm_tcgen05_bf16": ([P, P, P, I, I, I, I, P, P], I),
     "gi_sample": ([P, L, I, I, P, P, P, c_ulonglong, P, P, P, P], I),
     "gi_sample_chunks": ([I], I),

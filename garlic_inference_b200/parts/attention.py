@@ -13,12 +13,24 @@ q/k norm, the window and the softmax scale are parameters.
 """
 from __future__ import annotations
 
+import numpy as np
 import torch
 
 from ..cache import KVRequirement
 from ..ops import kernels, linear
 from ..weights.loader import TensorWant
 from .base import Mixer, register_part
+
+
+def query_runs(shape, rows: int) -> np.ndarray:
+    """The step's rows cut into runs of at most `rows` consecutive tokens of one sequence, the way the
+    tensor-core prompt kernels take their queries: int32 [n_runs, 4] = {slot, first row, rows, position of the
+    first row}.  The runs with the most keys to walk go first, so that the last blocks to start are short."""
+    runs = [(s, st + r0, min(rows, n - r0), p + r0)
+            for s, st, n, p in zip(shape.seq_slots, shape.seq_starts, shape.seq_lens, shape.seq_past)
+            for r0 in range(0, n, rows)]
+    runs.sort(key=lambda t: -(t[3] + t[2]))
+    return np.asarray(runs, dtype=np.int32).reshape(-1, 4)
 
 
 class GQAAttention(Mixer):
@@ -76,6 +88,24 @@ class GQAAttention(Mixer):
         o = self.attend(q, kv, ctx)
         return linear(o, self.w_o)
 
+    def _run_rows(self, kv) -> int:
+        """Height of the query runs the prompt kernel for this head size, type and page size takes (0: the
+        exact-order kernel, which needs none)."""
+        if kernels.tcgen05_attention_takes(self.rt.dtype, self.d, kv.page_size):
+            return 128
+        return 64 if kernels.mma_attention_takes(self.rt.dtype, self.d) else 0
+
+    def step_arrays(self, shape, cache):
+        rows = 0 if shape.all_single else self._run_rows(cache.kv)
+        return {f"query_runs_{rows}": lambda: query_runs(shape, rows)} if rows else {}
+
+    def _runs(self, ctx, rows: int) -> torch.Tensor:
+        runs = ctx.arrays.get(f"query_runs_{rows}")
+        if runs is None:                      # a context put together by hand: cut and copy here
+            runs = torch.from_numpy(query_runs(ctx, rows)).to(ctx.tok_pos.device)
+            ctx.arrays[f"query_runs_{rows}"] = runs
+        return runs
+
     def attend(self, q, kv, ctx):
         """Attention of q [n, n_q, d] over the cache; returns [n, n_q * d].
 
@@ -84,22 +114,22 @@ class GQAAttention(Mixer):
         16).  Otherwise bfloat16 with a head size the mma.sync kernels take: the split-KV kernel for single
         tokens, the flash kernel for runs.  Everything else (float32, other head sizes, larger groups in
         decode) goes to the exact-order kernel."""
-        if (not ctx.all_single and ctx.q_tiles128 is not None
-                and kernels.tcgen05_attention_takes(q.dtype, self.d, kv.page_size)):
-            return kernels.attention_prefill_tcgen05(q, kv.k_pool, kv.v_pool, kv.block_table, ctx.q_tiles128,
-                                                     self.scale, self.window or 0,
-                                                     rows_covered=ctx.n_tokens == sum(ctx.seq_lens))
-        if ctx.all_single and kernels.tcgen05_decode_takes(q.dtype, self.d, kv.page_size, self.n_q // self.n_kv):
-            return kernels.attention_decode_tcgen05(q, kv.k_pool, kv.v_pool, kv.block_table, ctx.tok_pos, ctx.tok_slot,
-                                                    self.scale, self.window or 0)
-        if kernels.mma_attention_takes(q.dtype, self.d):
-            if ctx.all_single and self.n_q // self.n_kv <= 16:
+        covered = (not ctx.all_single) and ctx.n_tokens == sum(ctx.seq_lens)
+        if ctx.all_single:
+            if kernels.tcgen05_decode_takes(q.dtype, self.d, kv.page_size, self.n_q // self.n_kv):
+                return kernels.attention_decode_tcgen05(q, kv.k_pool, kv.v_pool, kv.block_table, ctx.tok_pos,
+                                                        ctx.tok_slot, self.scale, self.window or 0)
+            if kernels.mma_attention_takes(q.dtype, self.d) and self.n_q // self.n_kv <= 16:
                 return kernels.attention_decode_bf16(q, kv.k_pool, kv.v_pool, kv.block_table, ctx.tok_pos,
                                                      ctx.tok_slot, self.scale, self.window or 0)
-            if not ctx.all_single and ctx.q_tiles is not None:
-                return kernels.attention_prefill_bf16(q, kv.k_pool, kv.v_pool, kv.block_table, ctx.q_tiles,
-                                                      self.scale, self.window or 0,
-                                                      rows_covered=ctx.n_tokens == sum(ctx.seq_lens))
+        elif ctx.seq_lens:
+            rows = self._run_rows(kv) if q.dtype == self.rt.dtype else 0
+            if rows == 128:
+                return kernels.attention_prefill_tcgen05(q, kv.k_pool, kv.v_pool, kv.block_table, self._runs(ctx, 128),
+                                                         self.scale, self.window or 0, rows_covered=covered)
+            if rows == 64:
+                return kernels.attention_prefill_bf16(q, kv.k_pool, kv.v_pool, kv.block_table, self._runs(ctx, 64),
+                                                      self.scale, self.window or 0, rows_covered=covered)
         return kernels.attention_generic(q, kv.k_pool, kv.v_pool, kv.block_table, ctx.tok_pos, ctx.tok_slot,
                                          self.scale, self.window or 0, ctx.status)
 

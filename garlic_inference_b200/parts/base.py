@@ -7,6 +7,7 @@ model builder looks the class up here, asks it which tensors it wants
 architecture it serves, and a new part needs no change in this package:
 register the class and name its kind in a plan.
 
+    class Part                   step_arrays(shape, cache) -> {name: function making an int32 array}
     class Mixer(Part)            cache_requirement() -> KVRequirement | StateRequirement | None
                                  step(x, ctx, cache, position, writes_cache) -> y        [n, hidden]
     class FeedForward(Part)      step(x, ctx) -> y                                        [n, hidden]
@@ -15,6 +16,18 @@ register the class and name its kind in a plan.
     class Block(Part)            step(delta, residual, ctx, cache, writes_cache) -> delta
     class Embedding(Part)        step(ctx) -> residual (float32)
     class Head(Part)             step(normed_rows) -> logits (float32)
+
+What a part may read of the batch.  Always, on the device: `ctx.tok_pos` and `ctx.tok_slot` (the
+position and the cache slot of every row; padding rows carry slot -1), the cache's tensors, and
+whatever the part asked for through `step_arrays` (`ctx.arrays[name]`).  On the host, unless the step
+is being recorded (`ctx.captured`): the per-sequence lists `seq_slots / seq_starts / seq_lens /
+seq_past`.  A decode step (`ctx.all_single`: one row per sequence) may be recorded into a CUDA graph
+and replayed for other sequences, so a part that declares `graph_safe = True` must run such a step
+from the device tensors alone.  A mixer with state of its own does that with
+`cache.state[ctx.tok_slot.long()]`: row i of the step belongs to slot `tok_slot[i]`, and slot -1
+addresses the state region's last row, a spare that no sequence owns, so padding rows read and write
+nothing that counts.  Steps that bring several tokens of a sequence are never recorded; there the part
+may walk the host lists.
 
 The hidden state between blocks is a pair: the float32 residual stream
 `residual` [n, hidden] and a pending `delta` in the activation type that has
@@ -59,6 +72,16 @@ class Runtime:
 
 
 @dataclass
+class StepShape:
+    """The host-side description of a step, before anything is on the device: one entry per sequence."""
+    seq_slots: list                     # slot of each sequence
+    seq_starts: list                    # first row of each sequence; a sequence's rows are contiguous
+    seq_lens: list                      # new tokens of each sequence
+    seq_past: list                      # positions already in the cache
+    all_single: bool                    # every sequence brings exactly one token
+
+
+@dataclass
 class StepContext:
     """One step's batch as the parts see it.  All tensors are on the device, int32."""
     n_tokens: int                       # rows run in this step (padding rows included)
@@ -72,10 +95,9 @@ class StepContext:
     seq_past: list = field(default_factory=list)       # positions already in the cache
     all_single: bool = False            # every sequence brings exactly one token (a decode step)
     max_kv_len: int = 0                 # longest sequence after this step (an upper bound is allowed)
-    # the rows cut into runs of at most 64 consecutive tokens of one sequence, int32 [n_runs, 4] =
-    # {slot, first row, rows, position of the first row}; None in decode steps
-    q_tiles: Optional[torch.Tensor] = None
-    q_tiles128: Optional[torch.Tensor] = None          # the same cut into runs of at most 128 rows
+    # int32 device tensors that parts asked for through `step_arrays`, by name (uploaded with the step's
+    # other arrays in one copy); empty in decode steps
+    arrays: dict = field(default_factory=dict)
     status: Optional[torch.Tensor] = None   # int32[1] error flag shared with the cache
     captured: bool = False              # the step is being recorded into a CUDA graph: the host-side
                                         # lists above are empty, everything must come from the tensors
@@ -98,6 +120,14 @@ class Part:
         """`load(local_name, out=None)` returns the device tensor (or copies it into `out`)."""
         self.params = dict(params)
         self.rt = rt
+
+    def step_arrays(self, shape: StepShape, cache) -> dict:
+        """Small int32 arrays this part wants on the device for the step that `shape` describes, as
+        {name: zero-argument function returning a numpy array}.  The engine makes each name once per step
+        (parts of one kind ask for the same names), copies them with the step's other arrays and hands
+        them over as `ctx.arrays[name]`, each starting on a 16-byte boundary.  `cache` is the part's view of
+        the cache.  Not called for recorded decode steps."""
+        return {}
 
 
 class Mixer(Part):
@@ -130,6 +160,10 @@ class PositionEncoding(Part):
 class Block(Part):
     def cache_requirement(self):
         return None
+
+    def step_arrays(self, shape: StepShape, cache) -> dict:
+        """The arrays of the block's parts (see `Part.step_arrays`)."""
+        return {}
 
     def step(self, delta, residual, ctx: StepContext, cache, writes_cache: bool = True):
         raise NotImplementedError

@@ -34,6 +34,9 @@ class PreNormResidualBlock(Block):
         return all(p.graph_safe for p in (self.mixer, self.feed_forward, self.norm_in, self.norm_post)) and \
             (self.position is None or self.position.graph_safe)
 
+    def step_arrays(self, shape, cache):
+        return {**self.mixer.step_arrays(shape, cache), **self.feed_forward.step_arrays(shape, cache)}
+
     def step(self, delta, residual, ctx, cache, writes_cache=True):
         x = self.norm_in.add_norm(delta, residual)
         a = self.mixer.step(x, ctx, cache, self.position, writes_cache)

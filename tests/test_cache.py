@@ -76,7 +76,7 @@ def test_groups_have_storage_of_their_own():
     assert win.block_table.data_ptr() != full.block_table.data_ptr()
     assert c.kv_view(1).k_pool.data_ptr() != full.k_pool.data_ptr()
     assert c.kv_view(3) is None and c.kv_view(4) is None
-    assert c.state_view(3).shape == (4, 3, 2) and c.state_bytes_per_slot == 24
+    assert c.state_view(3).shape == (4 + 1, 3, 2) and c.state_bytes_per_slot == 24     # a row per slot and a spare
     assert c.bytes_per_token() == 2 * 3 * 2 * 8 * 4
 
 

@@ -207,6 +207,45 @@ def test_gemm_streamk_bf16(m, n, k, out_dtype):
     assert int(_streamk_workspace(x.device)[1].abs().sum().item()) == 0, "a flag was left set"
 
 
+def test_a_bounded_wait_that_runs_out_is_reported_and_the_next_call_works(gpu_models):
+    """The stream-K product with the flags that announce partial sums held back (a switch of the kernel for this
+    test): the CTAs that hold the head of a cut tile poll 2,000 times for a flag that nothing sets, give up, record
+    code 34 and return.  The kernel ends (no hang), `Engine.check()` raises, the flag and the hand-over flags are
+    clean afterwards, and the same product then gives the right result."""
+    from garlic_inference_b200.ops.kernels import WaitRanOut, _streamk_workspace
+    g = torch.Generator(device=DEV).manual_seed(5)
+    x = torch.randn(8, 4096, generator=g, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(4096, 4096, generator=g, device=DEV) * 0.1).to(torch.bfloat16)     # 32 tiles over 148 CTAs: every tile is cut
+    ref = x.float() @ w.float().T
+    flag = K().tcgen05_error_flag(x.device)
+    flag.zero_()
+    model = gpu_models("A", "bfloat16")
+    model.engine.check()                                  # nothing pending
+    K().streamk_test_unanswered_flags(2000)
+    try:
+        K().gemm_streamk_bf16(x, w, torch.float32)
+        torch.cuda.synchronize()                          # comes back: the wait was bounded
+    finally:
+        K().streamk_test_unanswered_flags(0)
+    assert int(flag.item()) == 34
+    with pytest.raises(WaitRanOut, match="code 34"):
+        model.engine.check()
+    assert int(flag.item()) == 0 and int(_streamk_workspace(x.device)[1].abs().sum().item()) == 0
+    model.engine.check()                                  # reported once
+    out = K().gemm_streamk_bf16(x, w, torch.float32)
+    torch.cuda.synchronize()
+    assert int(flag.item()) == 0
+    torch.testing.assert_close(out, ref, rtol=1e-4, atol=2e-4 * math.sqrt(4096))
+    # flags that a kernel which gave up left set (announced, never answered) are cleared by the check as well
+    _streamk_workspace(x.device)[1][3] = 1
+    flag.fill_(33)
+    with pytest.raises(WaitRanOut, match="code 33"):
+        K().check_bounded_waits(x.device)
+    assert int(_streamk_workspace(x.device)[1].abs().sum().item()) == 0
+    out = K().gemm_streamk_bf16(x, w, torch.float32)
+    torch.testing.assert_close(out, ref, rtol=1e-4, atol=2e-4 * math.sqrt(4096))
+
+
 @pytest.mark.parametrize("m,inter,k", [(300, 128, 64), (300, 100, 64), (257, 7, 128), (2048, 320, 256), (513, 1000, 4096), (129, 136, 72), (1, 264, 1288),
                                        (1024, 12288, 512)])
 def test_gemm_tcgen05_swiglu_bf16(m, inter, k):

@@ -50,15 +50,17 @@ def test_every_cutting_agrees_with_the_plain_implementation(name, dtype, gpu_mod
 
     whole = tiny.run_trace_in_process(model, tiny.trace_whole(reqs))
     tiny.assert_covers(whole, reqs)
-    tiny.compare(whole, want, tol, f"{name} {dtype} whole")
+    worst = {"whole": tiny.compare(whole, want, tol, f"{name} {dtype} whole")}
 
     tail = tiny.run_trace_in_process(model, tiny.trace_tail_by_one(reqs, tail=32))
     tiny.assert_covers(tail, reqs)
-    tiny.compare(tail, want, tol, f"{name} {dtype} last 32 one by one")
+    worst["tail"] = tiny.compare(tail, want, tol, f"{name} {dtype} last 32 one by one")
 
     batched = tiny.run_trace_in_process(model, tiny.trace_batched(reqs, BATCHES, prompt_frac=0.5))
     tiny.assert_covers(batched, reqs)
-    tiny.compare(batched, want, tol, f"{name} {dtype} unequal batches")
+    worst["batched"] = tiny.compare(batched, want, tol, f"{name} {dtype} unequal batches")
+    print(f"WORST {name} {dtype} " + " ".join(f"{k}={v:.3e}" for k, v in worst.items()))
+    tiny.check_seen(name, dtype, max(worst.values()))
 
     cache = model.engine.cache
     assert cache.slots.n_free == cache.max_slots

@@ -106,10 +106,7 @@ def _attention_setup(dtype, window, n_q=6, n_kv=2, d=32, hidden=96, S=50, page=1
                            tok_pos=torch.arange(lo, hi, dtype=torch.int32, device=DEV),
                            tok_slot=torch.full((n,), slot, dtype=torch.int32, device=DEV),
                            seq_slots=[slot], seq_starts=[0], seq_lens=[n], seq_past=[lo], all_single=(n == 1),
-                           max_kv_len=hi, status=cache.status,
-                           q_tiles=None if n == 1 else torch.tensor(
-                               [(slot, r0, min(64, n - r0), lo + r0) for r0 in range(0, n, 64)],
-                               dtype=torch.int32, device=DEV))
+                           max_kv_len=hi, status=cache.status)
     return part, rope, cache, x.to(DEV), want, ctx_for
 
 
@@ -187,6 +184,7 @@ def _toy_classes():
 
     class RunningSumMixer(Mixer):
         kind = "toy_running_sum"
+        graph_safe = True              # a step of one token per sequence runs from the device tensors alone
 
         @classmethod
         def wanted(cls, params):
@@ -202,6 +200,13 @@ def _toy_classes():
             return StateRequirement((self.hidden,), torch.float32)
 
         def step(self, x, ctx, cache, position, writes_cache=True):
+            if ctx.all_single:
+                # one row per sequence, maybe recorded into a CUDA graph: row i belongs to slot tok_slot[i]; a
+                # padding row's slot is -1, the state region's spare last row
+                slots = ctx.tok_slot.long()
+                state = cache.state[slots] * self.decay + x.float()
+                cache.state[slots] = state
+                return (state * self.mix).to(x.dtype)
             out = torch.empty_like(x)
             for slot, start, n in zip(ctx.seq_slots, ctx.seq_starts, ctx.seq_lens):
                 state = cache.state[slot]
@@ -265,6 +270,8 @@ def test_a_toy_mixer_with_state_is_registered_built_and_stepped(dtype, tmp_path)
         got = tiny.run_trace_in_process(model, steps)
         tiny.assert_covers(got, reqs)
         tiny.compare(got, want, tiny.TOL[dtype], f"toy {dtype}")
+    # one layer with state of its own does not send the model back to launch-by-launch decoding
+    assert model.engine.graphs is not None and sorted(model.engine.graphs._graphs) == [1, 2]
 
 
 def _plain_layer(h, w, i, cfg, pos, kv=None):

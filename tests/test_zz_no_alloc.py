@@ -62,6 +62,18 @@ def test_static_scratch_entry_matches_the_allocating_one_twice_in_a_row():
         assert torch.isfinite(got.float()).all()
         torch.testing.assert_close(got.float(), want.float(), rtol=2e-2, atol=2e-2)
         assert torch.equal(got, want), "the same kernels on the same inputs: the same bits"
+        # the property the entry point exists for: a further call takes no device memory, from the driver or
+        # from torch's allocator (the output buffer is made before the reading)
+        n, n_pages = q.shape[0], k_pool.shape[0]
+        out = torch.empty((n, n_q * d), dtype=torch.bfloat16, device=DEV)
+        torch.cuda.synchronize()
+        free_before, reserved_before = torch.cuda.mem_get_info()[0], torch.cuda.memory_reserved()
+        rc = fn(q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), bt.data_ptr(), pos.data_ptr(), slot.data_ptr(),
+                out.data_ptr(), n, n_q, n_kv, d, page, bt.shape[1], n_pages, window, scale, splits,
+                torch.cuda.current_stream().cuda_stream)
+        torch.cuda.synchronize()
+        assert rc == 0 and torch.equal(out, want)
+        assert torch.cuda.mem_get_info()[0] == free_before and torch.cuda.memory_reserved() == reserved_before
 
 
 def test_static_scratch_entry_refuses_what_does_not_fit():

@@ -59,6 +59,22 @@ TINY = {
 TOL = {"float32": 1e-4, "bfloat16": 3e-2}
 
 
+# The worst error of the engine against the plain implementation that each configuration showed when these
+# numbers were recorded (all cuttings, relative to the largest logit).  A comparison may not exceed twice its
+# recorded value: the flat bounds above would let a regression of ten times pass.
+SEEN = {
+    "bfloat16": {},
+    "float32": {},
+}
+
+
+def check_seen(name: str, dtype: str, worst: float) -> None:
+    seen = SEEN[dtype].get(name)
+    if seen is not None:
+        assert worst <= 2 * seen, (f"{name} {dtype}: worst relative error {worst:.3e} is more than twice the "
+                                   f"{seen:.3e} recorded for this configuration")
+
+
 def make_config(name: str):
     from garlic_inference_b200 import Qwen3Config
     return Qwen3Config(**TINY[name]["cfg"])
