@@ -41,24 +41,26 @@ def peaks():
     if os.path.isfile(path):
         try:
             p = json.load(open(path))
-            return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"]), "source": "measured"}
+            return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"]),
+                    "bf16_tflops_sustained": float(p.get("bf16_tflops_sustained") or 0) or None, "source": "measured"}
         except (KeyError, ValueError, TypeError):
             pass
     return dict(FALLBACK_PEAKS)
 
 
 class ClockSampler:
-    """nvidia-smi in the background while a region is timed (reads only; nothing is set)."""
-    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    """nvidia-smi in the background while a region is timed (reads only; nothing is set).  Every sample carries
+    nvidia-smi's own wall-clock time, so that a summary can be taken over a part of the sampled time."""
+    QUERY = ("timestamp,clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap,power.draw")
 
-    def __init__(self, gpu_id: str):
-        self.gpu_id, self.proc, self.lines = gpu_id, None, []
+    def __init__(self, gpu_id: str, period_ms: int = 100):
+        self.gpu_id, self.period_ms, self.proc, self.lines = gpu_id, period_ms, None, []
 
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", self.gpu_id, f"--query-gpu={self.QUERY}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", str(self.period_ms)],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
@@ -76,21 +78,34 @@ class ClockSampler:
         self.lines += [l for l in out.splitlines() if l.strip()]
         self.proc = None
 
-    def summary(self):
-        sm, mx, reasons = [], [], set()
+    def summary(self, since: float = None, until: float = None):
+        """Median SM clock and the reasons seen, over all samples or over those taken between two time.time() values."""
+        import datetime
+        sm, mx, watts, reasons = [], [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for l in self.lines:
             f = [x.strip() for x in l.split(",")]
             try:
-                sm.append(float(f[0])), mx.append(float(f[1]))
+                if since is not None or until is not None:
+                    t = datetime.datetime.strptime(f[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                    if (since is not None and t < since) or (until is not None and t > until):
+                        continue
+                sm.append(float(f[1])), mx.append(float(f[2]))
             except (ValueError, IndexError):
                 continue
-            for name, v in zip(names, f[2:6]):
+            for name, v in zip(names, f[3:7]):
                 if v.lower() == "active":
                     reasons.add(name)
+            try:
+                watts.append(float(f[7]))
+            except (ValueError, IndexError):
+                pass
         if not sm:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
-        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+        out = {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+        if watts:
+            out["watts"] = statistics.median(watts)
+        return out
 
 
 def decode_step_bytes(cfg, n_layers, batch, context_tokens):
@@ -246,6 +261,69 @@ def reference_arm(args) -> int:
     return 0
 
 
+# the two larger workloads (layer sizes of Qwen3-14B and Qwen3-32B), run through `generate()`
+LARGER = {
+    "qwen3_14b": dict(cfg=dict(hidden_size=5120, num_hidden_layers=40, num_attention_heads=40, num_key_value_heads=8,
+                               head_dim=128, intermediate_size=17408, vocab_size=151936, rope_theta=1e6, rms_norm_eps=1e-6,
+                               max_position_embeddings=40960, tie_word_embeddings=False),
+                      batch=16, prompt=(256, 2048), new_tokens=512),
+    "qwen3_32b": dict(cfg=dict(hidden_size=5120, num_hidden_layers=64, num_attention_heads=64, num_key_value_heads=8,
+                               head_dim=128, intermediate_size=25600, vocab_size=151936, rope_theta=1e6, rms_norm_eps=1e-6,
+                               max_position_embeddings=40960, tie_word_embeddings=False),
+                      batch=32, prompt=(1024, 1024), new_tokens=1024),
+}
+
+
+def larger_workloads(first_model, pk, gpu_id) -> dict:
+    """Batch 16 with prompts uniform in [256, 2,048] then 512 decode steps at Qwen3-14B layer sizes; batch 32 with
+    prompts of 1,024 then 1,024 decode steps at Qwen3-32B layer sizes (65.5 GB of weights).  Random weights, all
+    layers, through `LanguageModel.generate` (host ids in and out).  Decode figures are over all decode steps."""
+    import gc
+    import torch
+    from garlic_inference_b200 import LanguageModel, Qwen3Config
+    # the benchmark model leaves the device before the larger ones arrive
+    first_model.engine.graphs = None
+    first_model.engine.cache = None
+    first_model.engine.model = None
+    first_model.model = None
+    gc.collect()
+    torch.cuda.empty_cache()
+    out = {}
+    gen = torch.Generator().manual_seed(1)
+    for name, w in LARGER.items():
+        cfg = Qwen3Config(**w["cfg"])
+        lo, hi = w["prompt"]
+        lens = [lo] * w["batch"] if lo == hi else torch.randint(lo, hi + 1, (w["batch"],), generator=gen).tolist()
+        prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=gen).tolist() for n in lens]
+        per_seq = [-(-(n + w["new_tokens"]) // 64) * 64 for n in lens]
+        try:
+            model = LanguageModel.from_random(cfg, seed=0, device=0, dtype="bfloat16", max_tokens=sum(per_seq) + 64)
+            model.generate([p[:64] for p in prompts], max_new_tokens=8)             # records the decode step, warms the path
+            clocks = ClockSampler(gpu_id, period_ms=50)
+            clocks.start()
+            toks = model.generate(prompts, max_new_tokens=w["new_tokens"])
+            clocks.stop()
+            st = model.last_stats
+            assert all(len(t) == w["new_tokens"] for t in toks)
+            steps = len(st.step_times) - 1                                          # decode steps (the first time is the prompt step's)
+            seconds = st.step_times[-1] - st.step_times[0]
+            ctx = sum(lens) / len(lens) + steps / 2
+            total_b, weight_b, kv_b = decode_step_bytes(w["cfg"], cfg.num_hidden_layers, w["batch"], ctx)
+            ms = 1e3 * seconds / steps
+            out[name] = {"batch": w["batch"], "prompt_tokens": sum(lens), "decode_steps": steps, "layers": cfg.num_hidden_layers,
+                         "decode_tok_s": w["batch"] * steps / seconds, "ms_per_step": ms,
+                         "prefill_tok_s": sum(lens) / st.prefill_seconds if st.prefill_seconds else None,
+                         "bytes_per_step": total_b, "hbm_frac": total_b / (ms / 1e3) / 1e9 / pk["hbm_gbs"],
+                         "weights_gb": weight_b / 1e9, "sm_mhz": clocks.summary().get("sm_mhz")}
+            model.engine.check()
+        except Exception as e:                                                      # a point that cannot run leaves the line standing
+            out[name] = {"unavailable": f"{type(e).__name__}: {e}"[:300]}
+        model = None
+        gc.collect()
+        torch.cuda.empty_cache()
+    return out
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -325,7 +403,9 @@ def main() -> int:
     # ---- prefill of 2,048 tokens --------------------------------------------------------------
     prompt = random_prompt(PREFILL_TOKENS)
     times = []
-    for i in range(3 + 3):
+    pre_clocks = ClockSampler(gpu_id, period_ms=20)
+    pre_clocks.start()
+    for i in range(3 + 5):
         s = eng.alloc_slot()
         torch.cuda.synchronize()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -336,10 +416,14 @@ def main() -> int:
         eng.free_slot(s)
         if i >= 3:
             times.append(a.elapsed_time(b))
+    pre_clocks.stop()
     pre_ms = statistics.median(times)
     pre_flops = prefill_flops(QWEN3_8B, n_layers, PREFILL_TOKENS)
     prefill = {"value": PREFILL_TOKENS / (pre_ms / 1e3), "tokens": PREFILL_TOKENS, "ms": pre_ms,
-               "frac": pre_flops / (pre_ms / 1e3) / (pk["bf16_tflops"] * 1e12)}
+               "frac": pre_flops / (pre_ms / 1e3) / (pk["bf16_tflops"] * 1e12),
+               "frac_of_sustained": (pre_flops / (pre_ms / 1e3) / (pk["bf16_tflops_sustained"] * 1e12)
+                                     if pk.get("bf16_tflops_sustained") else None),
+               "sm_mhz": pre_clocks.summary().get("sm_mhz")}
 
     # ---- decoding, timed on the device ----------------------------------------------------------
     clocks = ClockSampler(gpu_id)
@@ -358,15 +442,23 @@ def main() -> int:
     prompts = [random_prompt(CACHED) for _ in range(args.batch)]
     model.generate(prompts[:1], max_new_tokens=4)                           # warm the path
     up0 = eng.bytes_uploaded
-    clocks.start()
+    e2e_clocks = ClockSampler(gpu_id, period_ms=20)
+    wall_minus_perf = time.time() - time.perf_counter()
+    e2e_clocks.start()
     out = model.generate(prompts, max_new_tokens=W + K + 1)
-    clocks.stop()
+    e2e_clocks.stop()
     st = model.last_stats
     assert all(len(o) == W + K + 1 for o in out) and len(st.step_times) == W + K + 1
     e2e_seconds = st.step_times[-1] - st.step_times[-1 - K]
+    # the clock during the timed steps of this run (its prompt step of batch x 2,048 tokens comes right before them),
+    # so that ms x MHz of the two decode figures can be compared
+    e2e_clk = e2e_clocks.summary(since=st.step_times[-1 - K] + wall_minus_perf, until=st.step_times[-1] + wall_minus_perf)
     e2e = {"value": args.batch * K / e2e_seconds, "unit": "tokens/s",
            "h2d_bytes_per_step": (eng.bytes_uploaded - up0) / st.steps,
-           "d2h_bytes_per_step": 4 * args.batch}
+           "d2h_bytes_per_step": 4 * args.batch, "ms_per_step": 1e3 * e2e_seconds / K,
+           "sm_mhz": e2e_clk.get("sm_mhz"), "watts": e2e_clk.get("watts")}
+    page_size = eng.cache.page_size
+    workloads = {} if args.no_points else larger_workloads(model, pk, gpu_id)
 
     line = {
         "metric": f"decode tok/s at batch {args.batch} (Qwen3-8B layer sizes, {CACHED} cached tokens per sequence)",
@@ -377,7 +469,7 @@ def main() -> int:
                    "cached_tokens": CACHED, "parallelism": "none (1 GPU)", "layers_run": n_layers,
                    "layers_config": QWEN3_8B["num_hidden_layers"], "hidden_size": 4096, "n_heads": 32,
                    "n_kv_heads": 8, "head_dim": 128, "intermediate_size": 12288, "vocab_size": 151936,
-                   "page_size": eng.cache.page_size, "sampling": "greedy on the device",
+                   "page_size": page_size, "sampling": "greedy on the device",
                    "l2": "inputs exceed L2: a step reads %.1f GB of weights" % (weight_b / 1e9)},
         "clocks": clocks.summary(),
         "e2e": e2e,
@@ -386,6 +478,7 @@ def main() -> int:
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": achieved / pk["hbm_gbs"], "bytes_per_step": total_b, "peaks": pk["source"]},
         "points": points,
+        "workloads": workloads,
     }
     print(json.dumps(line))
     return 0
