@@ -43,6 +43,11 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--max-tokens", type=int, default=None,
                     help="cache size in tokens (default: what the given prompts need)")
     ap.add_argument("--max-batch", type=int, default=None, help="most requests in one batch")
+    ap.add_argument("--max-slots", type=int, default=None,
+                    help="most requests the cache can hold at once (default: one per 64 tokens of the cache)")
+    ap.add_argument("--print-logits", type=int, default=0, metavar="N",
+                    help="before generating, run each prompt once and print the N largest logits (id:value) at its "
+                         "last position, for comparing numbers with another implementation")
     ap.add_argument("--page-size", type=int, default=64)
     ap.add_argument("--device", type=int, default=0)
     return ap
@@ -72,10 +77,19 @@ def main(argv=None) -> int:
     need = sum(tokens_held(len(p), args.max_new_tokens, max_pos) for p in prompts[:args.max_batch or len(prompts)])
     if args.random_weights:
         model = AutoModel.from_random(load_config(args.model_dir), seed=args.weights_seed, device=args.device,
-                                      dtype=args.dtype, max_tokens=args.max_tokens or need, page_size=args.page_size)
+                                      dtype=args.dtype, max_tokens=args.max_tokens or need, page_size=args.page_size,
+                                      max_slots=args.max_slots)
     else:
         model = AutoModel.from_pretrained(args.model_dir, device=args.device, dtype=args.dtype,
-                                          max_tokens=args.max_tokens or need, page_size=args.page_size)
+                                          max_tokens=args.max_tokens or need, page_size=args.page_size,
+                                          max_slots=args.max_slots)
+    if args.print_logits > 0:
+        for i, p in enumerate(prompts):
+            slot = model.alloc_slot()
+            row = model.step([(slot, p, [len(p) - 1])])[0]
+            model.free_slot(slot)
+            top = row.topk(min(args.print_logits, row.numel()))
+            print(f"Logits {i}: " + " ".join(f"{int(t)}:{float(v):.6g}" for v, t in zip(top.values.tolist(), top.indices.tolist())))
     stop = None if args.stop_ids is None else parse_ids(args.stop_ids)
     out = model.generate(prompts, max_new_tokens=args.max_new_tokens, temperature=args.temperature,
                          seed=args.seed, stop_token_ids=stop, max_batch=args.max_batch)

@@ -37,7 +37,7 @@ class BuildError(RuntimeError):
 
 def timeline_build() -> bool:
     """GARLIC_B200_TIMELINE=1: a build of its own (folder `_build_timeline`) whose kernels note when they start
-    and when they are released (common.cuh); `python -m garlic_inference_b200.ops.microbench timeline` reads it."""
+    and when they are released (common.cuh); `python -m garlic_inference_b200.engine.timeline` reads it."""
     return os.environ.get("GARLIC_B200_TIMELINE", "0") == "1"
 
 

@@ -48,10 +48,11 @@ class LanguageModel:
     """A model on the GPU with its cache: `step` for given tokens, `generate` for sampled ones."""
 
     def __init__(self, config, model: DecoderModel, max_tokens: int, page_size: int = 64,
-                 default_stop_ids: Sequence[int] = (), use_graphs: bool = True):
+                 default_stop_ids: Sequence[int] = (), use_graphs: bool = True, max_slots: Optional[int] = None):
         self.config = config
         self.model = model
-        self.engine = Engine(model, max_tokens=max_tokens, page_size=page_size, use_graphs=use_graphs)
+        self.engine = Engine(model, max_tokens=max_tokens, page_size=page_size, use_graphs=use_graphs,
+                             max_slots=max_slots)
         self.sampler = Sampler(model.rt.device)
         self.default_stop_ids = tuple(default_stop_ids)
         self.last_stats = None
@@ -60,7 +61,9 @@ class LanguageModel:
     # ---- construction ----------------------------------------------------------------
     @classmethod
     def from_pretrained(cls, model_dir, device=0, dtype="bfloat16", max_tokens: int = 8192,
-                        page_size: int = 64, use_graphs: bool = True) -> "LanguageModel":
+                        page_size: int = 64, use_graphs: bool = True, max_slots: Optional[int] = None) -> "LanguageModel":
+        """`max_tokens` sizes the cache (tokens that live requests hold, each request's count in units of 64);
+        `max_slots` is the most requests that can be live at once (default: one per 64 tokens of the cache)."""
         from ..ops import require_gpu
         dev = _device(device)
         if dev.type == "cuda":
@@ -76,12 +79,12 @@ class LanguageModel:
         if gen_cfg.is_file():
             eos = json.loads(gen_cfg.read_text()).get("eos_token_id")
             stop = tuple(eos) if isinstance(eos, list) else (() if eos is None else (int(eos),))
-        return cls(config, model, max_tokens, page_size, stop, use_graphs)
+        return cls(config, model, max_tokens, page_size, stop, use_graphs, max_slots)
 
     @classmethod
     def from_random(cls, config, seed: int = 0, device=0, dtype="bfloat16", max_tokens: int = 8192,
                     page_size: int = 64, std: float = 0.02, norm_std: float = 0.0,
-                    use_graphs: bool = True) -> "LanguageModel":
+                    use_graphs: bool = True, max_slots: Optional[int] = None) -> "LanguageModel":
         """Random weights made on the device (bfloat16 storage), nothing written to disk."""
         from ..ops import require_gpu
         dev = _device(device)
@@ -92,7 +95,7 @@ class LanguageModel:
         source = RandomSource(wanted_tensors(plan), seed=seed, std=std, norm_std=norm_std,
                               dtype=torch.bfloat16, device=dev)
         return cls(config, DecoderModel(plan, source, Runtime(engine_dtype(dtype), dev)), max_tokens, page_size,
-                   use_graphs=use_graphs)
+                   use_graphs=use_graphs, max_slots=max_slots)
 
     # ---- stepping ----------------------------------------------------------------------
     def alloc_slot(self) -> int:

@@ -139,3 +139,23 @@ def test_timeline_of_a_recorded_step(model_dirs):
     head = r.stdout.splitlines()[0]
     assert "kernels" in head and "a layer is 9 kernels" in head, r.stdout[:2000]
     assert "a layer:" in r.stdout
+
+
+def test_command_line_print_logits_and_max_slots(model_dirs):
+    """--print-logits N prints the N largest logits at each prompt's last position before generating;
+    --max-slots 1 lets one request live at a time, so two prompts run as two batches with the same ids."""
+    cmd = [sys.executable, str(tiny.REPO / "bin" / "runner"), str(model_dirs("A")), "--max-new-tokens", "4",
+           "--dtype", "float32", "--prompt-ids", "1,2,3", "--prompt-ids", "40,41", "--print-logits", "3",
+           "--max-slots", "1", "--max-tokens", "128"]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-3000:]
+    lines = r.stdout.strip().splitlines()
+    cfg, w = plain.read_model_dir(model_dirs("A"))
+    for i, prompt in enumerate(([1, 2, 3], [40, 41])):
+        assert lines[i].startswith(f"Logits {i}: ")
+        pairs = [p.split(":") for p in lines[i].split(": ", 1)[1].split()]
+        want = plain.forward(cfg, w, prompt)[-1]
+        top = want.topk(3)
+        assert [int(t) for t, _ in pairs] == top.indices.tolist()
+        assert all(abs(float(v) - float(x)) < 1e-4 * float(want.abs().max()) for (_, v), x in zip(pairs, top.values))
+        assert [int(t) for t in lines[2 + i].split()] == plain.greedy(cfg, w, prompt, 4)

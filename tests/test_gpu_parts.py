@@ -146,7 +146,7 @@ def test_block_embedding_and_head_parts(dtype, model_dirs):
     model = DecoderModel(cfg_obj.plan(), Checkpoint(d), rt_for(dtype))
     ids = np.random.default_rng(5).integers(0, 1000, size=21)
     S = len(ids)
-    cache = PagedCache(model.cache_requirements(), max_tokens=64, max_positions=640, dtype=dtype, device=DEV, page_size=16)
+    cache = PagedCache(model.cache_requirements(), max_tokens=64, max_positions=256, dtype=dtype, device=DEV, page_size=16)
     s = cache.alloc_slot()
     cache.prepare([s], [S])
     ctx = StepContext(n_tokens=S, tokens=torch.tensor(ids, dtype=torch.int32, device=DEV),

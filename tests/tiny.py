@@ -26,6 +26,11 @@ TINY = {
               seed=0, std=0.02, norm_std=0.1),
     "B": dict(cfg=dict(hidden_size=96, num_hidden_layers=3, num_attention_heads=6, num_key_value_heads=1,
                        head_dim=32, intermediate_size=256, vocab_size=1000, rope_theta=1e6, rms_norm_eps=1e-5,
+                       max_position_embeddings=256, tie_word_embeddings=False),
+              seed=1, std=0.05, norm_std=0.2),
+    # B with room for 640 positions (the same weights: no tensor depends on the limit), for long decoding
+    "F": dict(cfg=dict(hidden_size=96, num_hidden_layers=3, num_attention_heads=6, num_key_value_heads=1,
+                       head_dim=32, intermediate_size=256, vocab_size=1000, rope_theta=1e6, rms_norm_eps=1e-5,
                        max_position_embeddings=640, tie_word_embeddings=False),
               seed=1, std=0.05, norm_std=0.2),
     "C": dict(cfg=dict(hidden_size=80, num_hidden_layers=4, num_attention_heads=5, num_key_value_heads=5,
