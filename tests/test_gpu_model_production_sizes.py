@@ -77,3 +77,28 @@ def test_batches_of_many_sequences_at_the_benchmark_s_layer_sizes(n, tmp_path_fa
     worst = tiny.compare(got, want, tiny.TOL["bfloat16"], f"8B-size layer, bfloat16, batch of {n}")
     print(f"8B-size layer, batch of {n}: worst relative error {worst:.3e}")
     assert max(model.engine.graphs._graphs) == 1 << (n - 1).bit_length()
+
+
+def test_the_benchmark_model_s_first_two_layers_from_random(tmp_path_factory):
+    """What bench.py times is `AutoModel.from_random` at Qwen3-8B sizes.  Its random weights depend on (seed, tensor
+    name, index) alone, so the same model can be written to a folder and read by the plain implementation: two
+    layers of it, the full vocabulary of 151,936, a prompt of 300 tokens and 8 decode steps."""
+    import numpy as np
+    from garlic_inference_b200 import AutoModel, Qwen3Config, write_random_model
+    cfg = Qwen3Config(hidden_size=4096, num_hidden_layers=2, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+                      intermediate_size=12288, vocab_size=151936, rope_theta=1e6, rms_norm_eps=1e-6,
+                      max_position_embeddings=40960, tie_word_embeddings=False)
+    model = AutoModel.from_random(cfg, seed=0, device=0, dtype="bfloat16", max_tokens=512)      # as bench.py makes it
+    folder = write_random_model(tmp_path_factory.mktemp("bench_2_layers"), cfg, seed=0, device="cuda")
+    reqs = tiny.random_requests(cfg.vocab_size, [308], seed=9)
+    want = tiny.plain_logits(folder, reqs)
+    steps = tiny.trace_tail_by_one(reqs, tail=8)
+    got = tiny.run_trace_in_process(model, steps)
+    tiny.assert_covers(got, reqs)
+    worst = tiny.compare(got, want, tiny.TOL["bfloat16"], "two layers of the benchmark model, bfloat16")
+    print(f"two layers of the benchmark model: worst relative error {worst:.3e}")
+    assert worst > 1e-5, "bfloat16 cannot be this exact"
+    top = np.stack([got["r0"][p] for p in range(308)]).argmax(1)
+    margin = np.sort(want["r0"], axis=1)
+    sure = (margin[:, -1] - margin[:, -2]) > 2 * tiny.TOL["bfloat16"] * np.abs(want["r0"]).max()
+    assert (top[sure] == want["r0"].argmax(1)[sure]).all()
