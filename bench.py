@@ -324,6 +324,51 @@ def larger_workloads(first_model, pk, gpu_id) -> dict:
     return out
 
 
+def study_prefill_clocks(model, prompt, gpu_id, flops) -> int:
+    """How a prompt step's time follows the clock: the first steps of a burst run at the full clock, then the power
+    cap pulls the clock down and the step time goes up with it."""
+    import datetime
+    import torch
+    eng = model.engine
+    clocks = ClockSampler(gpu_id, period_ms=20)
+    slots = [eng.alloc_slot() for _ in range(2)]
+    model.step([(slots[0], prompt, [len(prompt) - 1])])                     # warm the path
+    eng.free_slot(slots[0])
+    torch.cuda.synchronize()
+    time.sleep(1.0)                                                         # let the GPU rest: the burst starts cool
+    clocks.start()
+    time.sleep(0.1)
+    rows, events = [], []
+    t_wall0 = time.time()
+    for i in range(40):
+        s = eng.alloc_slot()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        model.step([(s, prompt, [len(prompt) - 1])])
+        b.record()
+        eng.free_slot(s)
+        events.append((a, b))
+    torch.cuda.synchronize()
+    t_wall1 = time.time()
+    clocks.stop()
+    samples = []
+    for l in clocks.lines:
+        f = [x.strip() for x in l.split(",")]
+        try:
+            samples.append((datetime.datetime.strptime(f[0], "%Y/%m/%d %H:%M:%S.%f").timestamp(), float(f[1]), float(f[7])))
+        except (ValueError, IndexError):
+            pass
+    ms = [a.elapsed_time(b) for a, b in events]
+    t = t_wall0
+    print("step   ms     TFLOP/s   sm MHz   W      ms x GHz")
+    for i, m in enumerate(ms):
+        mid = t + m / 2e3
+        near = min(samples, key=lambda s: abs(s[0] - mid)) if samples else (0, float("nan"), float("nan"))
+        print(f"{i:3d}  {m:6.2f}  {flops / m / 1e9:8.0f}  {near[1]:7.0f}  {near[2]:5.0f}  {m * near[1] / 1e3:7.2f}")
+        t += (t_wall1 - t_wall0) / len(ms)
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -334,6 +379,9 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration's 36 "
                     "(layer sizes stay); the JSON names both numbers")
     ap.add_argument("--no-points", action="store_true", help="skip decoding at batch 1 and 64")
+    ap.add_argument("--study", default=None, choices=["prefill-clocks"],
+                    help="prefill-clocks: 40 prompt steps of 2,048 tokens back to back with the clock and the power "
+                         "sampled every 20 ms; prints a table and no JSON line")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -399,6 +447,10 @@ def main() -> int:
         for s in slots:
             eng.free_slot(s)
         return batch * K / (ms / 1e3), ms / K, launched
+
+    if args.study == "prefill-clocks":
+        return study_prefill_clocks(model, random_prompt(PREFILL_TOKENS), gpu_id,
+                                    prefill_flops(QWEN3_8B, n_layers, PREFILL_TOKENS))
 
     # ---- prefill of 2,048 tokens --------------------------------------------------------------
     prompt = random_prompt(PREFILL_TOKENS)
