@@ -163,6 +163,10 @@ int main(int argc, char** argv) {
         if (dump) dump_logits(dump, logits);
         auto ret = argmax(logits, x);
         for (int b = 0; b < B; ++b) last[b] = ret[(size_t)b * C + C - 1];
+        // upstream frees its per-pass buffers with cudaFreeAsync on its load stream and never synchronises that
+        // stream, so the driver gives nothing back; between prompt chunks (argmax has just drained the compute
+        // stream, and the decode loop below is left as upstream runs it) this wait lets the frees take effect
+        cudaStreamSynchronize(get_load_offload_stream());
     }
     const double free_after_prompt = free_gb();
     Tensor x({B, 1}, CUDA_R_32U, 0);
