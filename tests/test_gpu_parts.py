@@ -455,3 +455,126 @@ def test_a_toy_routed_feed_forward_and_learned_positions_are_registered_built_an
         got = tiny.run_trace_in_process(model, steps)
         tiny.assert_covers(got, reqs)
         tiny.compare(got, want, tiny.TOL["float32"], "toy routed float32")
+
+
+# ---------------------------------------------------------------------------------------------------
+# generality: a toy norm, a toy block arrangement and a partial rotation, registered from outside
+# ---------------------------------------------------------------------------------------------------
+def _toy_parallel_classes():
+    """The two remaining kinds of part, defined here: a norm that subtracts the mean and has a bias, and a block
+    that runs its mixer and its feed-forward side by side on one normed input (h += attention(x) + ffn(x)); and the
+    built-in rotary part asked to rotate only the first half of every head.  The framework's files know none of it."""
+    import dataclasses
+    from garlic_inference_b200 import Qwen3Config, register_architecture, register_part
+    from garlic_inference_b200.config.base import LayerSpec, PartSpec
+    from garlic_inference_b200.parts import Block, Norm
+    from garlic_inference_b200.weights import TensorWant
+
+    class MeanNorm(Norm):
+        kind = "toy_mean_norm"
+        graph_safe = True                   # device tensors only
+
+        @classmethod
+        def wanted(cls, params):
+            return {"weight": TensorWant((params["size"],), "norm"), "bias": TensorWant((params["size"],))}
+
+        def __init__(self, params, load, rt):
+            super().__init__(params, load, rt)
+            self.eps = params["eps"]
+            self.weight, self.bias = load("weight").float(), load("bias").float()
+
+        def add_norm(self, delta, residual, rows=None, write_residual=True):
+            s = residual if rows is None else residual.index_select(0, rows.long())
+            if delta is not None:
+                s = s + (delta if rows is None else delta.index_select(0, rows.long())).float()
+                if write_residual and rows is None:
+                    residual.copy_(s)
+            mu = s.mean(-1, keepdim=True)
+            var = ((s - mu) ** 2).mean(-1, keepdim=True)
+            return ((s - mu) * torch.rsqrt(var + self.eps) * self.weight + self.bias).to(self.rt.dtype)
+
+    class ParallelBlock(Block):
+        kind = "toy_parallel"
+
+        def __init__(self, mixer, feed_forward, norms, position, rt):
+            self.rt, self.mixer, self.feed_forward, self.position = rt, mixer, feed_forward, position
+            self.norm = norms["input"]
+
+        @property
+        def graph_safe(self):
+            return all(p.graph_safe for p in (self.mixer, self.feed_forward, self.norm, self.position))
+
+        def cache_requirement(self):
+            return self.mixer.cache_requirement()
+
+        def step_arrays(self, shape, cache):
+            return {**self.mixer.step_arrays(shape, cache), **self.feed_forward.step_arrays(shape, cache)}
+
+        def step(self, delta, residual, ctx, cache, writes_cache=True):
+            x = self.norm.add_norm(delta, residual)
+            return self.mixer.step(x, ctx, cache, self.position, writes_cache) + self.feed_forward.step(x, ctx)
+
+    class ParallelConfig(Qwen3Config):
+        def plan(self):
+            base = super().plan()
+            ln = lambda prefix: PartSpec("toy_mean_norm", dict(size=self.hidden_size, eps=self.rms_norm_eps),
+                                         dict(weight=prefix + ".weight", bias=prefix + ".bias"))
+            layers = tuple(LayerSpec("toy_parallel", l.mixer, l.feed_forward,
+                                     {"input": ln(f"model.layers.{i}.input_layernorm")}, position="rotary")
+                           for i, l in enumerate(base.layers))
+            positions = {"rotary": dataclasses.replace(
+                base.positions["rotary"], params={**base.positions["rotary"].params, "rotary_dim": self.head_dim // 2})}
+            return dataclasses.replace(base, architecture="ToyParallelForCausalLM", layers=layers, positions=positions,
+                                       final_norm=ln("model.norm"))
+
+    register_part("toy_mean_norm", MeanNorm)
+    register_part("toy_parallel", ParallelBlock)
+    register_architecture("ToyParallelForCausalLM", ParallelConfig)
+    return ParallelConfig
+
+
+def _plain_parallel_forward(cfg, w, ids):
+    ids = torch.as_tensor(ids)
+    n = len(ids)
+    pos = torch.arange(n)
+    d, n_q, n_kv, eps, theta = (cfg[k] for k in ("head_dim", "num_attention_heads", "num_key_value_heads",
+                                                 "rms_norm_eps", "rope_theta"))
+
+    def mean_norm(x, prefix):
+        mu = x.mean(-1, keepdim=True)
+        var = ((x - mu) ** 2).mean(-1, keepdim=True)
+        return (x - mu) * torch.rsqrt(var + eps) * w[prefix + ".weight"] + w[prefix + ".bias"]
+
+    def half_rope(x):                        # the first d/2 of every head rotated (angles theta^(-2i/(d/2))), the rest as it is
+        return torch.cat([plain.apply_rope(x[..., : d // 2], pos, theta), x[..., d // 2:]], dim=-1)
+
+    h = plain.embed(ids, w["model.embed_tokens.weight"])
+    for i in range(cfg["num_hidden_layers"]):
+        p = f"model.layers.{i}."
+        x = mean_norm(h, p + "input_layernorm")
+        q = plain.rms_norm((x @ w[p + "self_attn.q_proj.weight"].T).view(n, n_q, d), w[p + "self_attn.q_norm.weight"], eps)
+        k = plain.rms_norm((x @ w[p + "self_attn.k_proj.weight"].T).view(n, n_kv, d), w[p + "self_attn.k_norm.weight"], eps)
+        v = (x @ w[p + "self_attn.v_proj.weight"].T).view(n, n_kv, d)
+        a = plain.attention_scores(half_rope(q), half_rope(k), v).reshape(n, n_q * d) @ w[p + "self_attn.o_proj.weight"].T
+        h = h + a + plain.swiglu_mlp(x, w, p + "mlp.")
+    return mean_norm(h, "model.norm") @ w["lm_head.weight"].T
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_toy_norm_a_toy_block_and_a_partial_rotation(dtype, tmp_path):
+    from garlic_inference_b200 import AutoModel, write_random_model
+    ParallelConfig = _toy_parallel_classes()
+    cfg_obj = ParallelConfig(**{**tiny.TINY["B"]["cfg"], "num_hidden_layers": 2, "architectures": ["ToyParallelForCausalLM"]})
+    d = write_random_model(tmp_path / "parallel", cfg_obj, seed=12, std=0.05, norm_std=0.2)
+    model = AutoModel.from_pretrained(d, device=0, dtype=dtype, max_tokens=512, page_size=16)
+    assert type(model.config) is ParallelConfig
+    cfg, w = plain.read_model_dir(d)
+    assert "model.layers.1.input_layernorm.bias" in w and "model.layers.1.post_attention_layernorm.weight" not in w
+    reqs = tiny.random_requests(1000, [45, 8, 70, 33], seed=51)
+    want = {rid: _plain_parallel_forward(cfg, w, t).numpy() for rid, t in reqs.items()}
+    for steps in (tiny.trace_whole(reqs), tiny.trace_tail_by_one(reqs, tail=32),
+                  tiny.trace_batched(reqs, [["r0", "r1"], ["r2", "r3"]])):
+        got = tiny.run_trace_in_process(model, steps)
+        tiny.assert_covers(got, reqs)
+        tiny.compare(got, want, tiny.TOL[dtype], f"toy parallel {dtype}")
+    assert model.engine.graphs is not None and model.engine.graphs._graphs, "its decode steps were recorded"
