@@ -407,7 +407,9 @@ def main() -> int:
     gpu_id = "GPU-" + str(props.uuid) if getattr(props, "uuid", None) else "0"
     batches = [args.batch] + ([] if args.no_points else [1, 64])
     per_seq = -(-(CACHED + W + K + 8) // 64) * 64
-    max_tokens = max(max(batches) * per_seq, -(-PREFILL_TOKENS // 64) * 64 * 2)
+    long_points = [] if args.no_points else [(8, 8192), (1, 32768)]          # (batch, cached tokens): longer contexts
+    max_tokens = max([max(batches) * per_seq, -(-PREFILL_TOKENS // 64) * 64 * 2] +
+                     [b * (-(-(c + W + K + 8) // 64) * 64) for b, c in long_points])
     model = LanguageModel.from_random(cfg, seed=0, device=0, dtype="bfloat16", max_tokens=max_tokens)
     eng, sampler = model.engine, model.sampler
     gen = torch.Generator().manual_seed(0)
@@ -416,18 +418,18 @@ def main() -> int:
     def random_prompt(n):
         return torch.randint(0, cfg.vocab_size, (n,), generator=gen).tolist()
 
-    def fill(batch):
-        """`batch` slots, each holding CACHED tokens after a real prefill; returns slots and next tokens."""
+    def fill(batch, cached=CACHED):
+        """`batch` slots, each holding `cached` tokens after a real prefill; returns slots and next tokens."""
         slots, firsts = [], []
         for _ in range(batch):
             s = eng.alloc_slot()
-            logits = model.step([(s, random_prompt(CACHED), [CACHED - 1])])
+            logits = model.step([(s, random_prompt(cached), [cached - 1])])
             firsts.append(sampler.sample(logits, greedy, [0], [0]))
             slots.append(s)
         return slots, torch.cat(firsts)
 
-    def time_decode(batch, clocks=None):
-        slots, toks = fill(batch)
+    def time_decode(batch, clocks=None, cached=CACHED):
+        slots, toks = fill(batch, cached)
         for _ in range(W):
             toks = sampler.sample(eng.step_decode_device(slots, toks), greedy, slots, slots)
         torch.cuda.synchronize()
@@ -487,6 +489,11 @@ def main() -> int:
     if not args.no_points:
         for b in (1, 64):
             points[f"decode_b{b}"] = time_decode(b)[0]
+        for b, c in long_points:                         # the same through the engine at longer contexts, with the
+            tok_s, ms, _ = time_decode(b, cached=c)      # fraction of the measured copy bandwidth the step's bytes reach
+            step_b = decode_step_bytes(QWEN3_8B, n_layers, b, c + W + (K + 1) / 2)[0]
+            points[f"decode_b{b}_ctx{c}"] = tok_s
+            points[f"decode_b{b}_ctx{c}_hbm_frac"] = step_b / (ms / 1e3) / 1e9 / pk["hbm_gbs"]
 
     # ---- the same through the entry point: host ids in, host ids out, every step ------------------
     # W + K + 1 tokens per request; the clock runs over the last K steps (the W before them are the warm-up,
