@@ -76,7 +76,8 @@ def compile_one(nvcc: str, src: Path, rel: str, obj: Path) -> tuple[str, float, 
 
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--src", default=os.environ.get("GARLIC_REFERENCE_SRC", "/root/reference"))
+    ap.add_argument("--src", default=os.environ.get("GARLIC_REFERENCE_SRC", str(HERE.parent.parent / "reference")),
+                    help="upstream's checkout (default: $GARLIC_REFERENCE_SRC, else a folder `reference` beside this repository)")
     ap.add_argument("--out", default=str(HERE / "_ref"))
     ap.add_argument("--jobs", type=int, default=max(1, (os.cpu_count() or 2) - 1))
     ap.add_argument("--force", action="store_true", help="recompile objects that exist")

@@ -171,7 +171,7 @@ def reference_arm(args) -> int:
         return 0
 
     if not os.path.isfile(REFERENCE_RUNNER):
-        src = os.environ.get("GARLIC_REFERENCE_SRC", "/root/reference")
+        src = os.environ.get("GARLIC_REFERENCE_SRC", os.path.join(os.path.dirname(ROOT), "reference"))
         if not os.path.isdir(src):
             return unavailable("baseline/_ref/bin/reference_runner is not built and there is no upstream checkout "
                                "here to build it from (baseline/build_reference.py)")
