@@ -317,3 +317,17 @@ def test_gemv_products_in_the_model(model_dirs, plain_cache, monkeypatch):
     got = tiny.run_trace_in_process(model, tiny.trace_tail_by_one(reqs, tail=32))
     tiny.assert_covers(got, reqs)
     tiny.compare(got, want, tiny.TOL["bfloat16"], "D bfloat16 with gemv products")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_step_by_step_against_the_plain_model_with_the_same_interface(dtype, gpu_models, model_dirs):
+    """The engine and the plain model behind the same stepping interface (tests/plain_stepper.py) replay one
+    schedule side by side: unequal prompts in one step, single tokens, a request that ends early, a slot used
+    again, a mixed step.  Every step's logits are compared as the step returns them."""
+    from plain_stepper import PlainStepper, first_step_that_differs
+    vocab = tiny.TINY["C"]["cfg"]["vocab_size"]
+    reqs = tiny.random_requests(vocab, [60, 23, 90, 41], seed=77)
+    steps = tiny.trace_batched(reqs, [["r0", "r1", "r2"], ["r3", "r1"]], prompt_frac=0.6)
+    model = gpu_models("C", dtype, max_tokens=4096, page_size=16)
+    bad = first_step_that_differs(model, PlainStepper(model_dirs("C")), steps, tiny.TOL[dtype])
+    assert bad is None, f"step {bad[0]} is the first that differs (relative error {bad[1]:.3e})"

@@ -1,4 +1,5 @@
 """The plain implementation checked against hand-computed values and its own invariants (CPU)."""
+import pytest
 import math
 
 import numpy as np
@@ -87,3 +88,24 @@ def test_greedy_matches_forward(tmp_path):
     assert len(new) == 4
     assert new[1] == int(plain.forward(cfg, w, [5, 6, 7, new[0]])[-1].argmax())
     assert plain.greedy(cfg, w, [5, 6, 7], 4, stop_ids=(new[1],)) == new[:2]
+
+
+def test_the_plain_model_behind_the_stepping_interface_replays_every_cutting(tmp_path):
+    """`PlainStepper` (alloc_slot / step / free_slot, no cache) replays the three cuttings the engine is tested with;
+    every (request, position) equals the whole-sequence logits.  This also checks the trace builders and `collect`
+    themselves, on the CPU."""
+    from plain_stepper import PlainStepper
+    d = tiny.write_model("A", tmp_path / "A")
+    reqs = tiny.random_requests(512, [9, 40, 3, 17], seed=5)
+    want = tiny.plain_logits(d, reqs)
+    stepper = PlainStepper(d)
+    for steps in (tiny.trace_whole(reqs), tiny.trace_tail_by_one(reqs, tail=8),
+                  tiny.trace_batched(reqs, [["r0", "r1"], ["r2", "r3"]], prompt_frac=0.4)):
+        got = tiny.run_trace_in_process(stepper, steps)
+        tiny.assert_covers(got, reqs)
+        assert tiny.compare(got, want, 1e-6, "plain stepper") < 1e-6
+        assert stepper.tokens == {}, "a slot was not given back"
+    s = stepper.alloc_slot()
+    stepper.free_slot(s)
+    with pytest.raises(KeyError):
+        stepper.free_slot(s)
