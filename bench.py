@@ -379,6 +379,9 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration's 36 "
                     "(layer sizes stay); the JSON names both numbers")
     ap.add_argument("--no-points", action="store_true", help="skip decoding at batch 1 and 64")
+    ap.add_argument("--write-model", default=None, metavar="DIR",
+                    help="with --impl reference: only write the model folder that arm uses (tied head, --layers of the 36) "
+                         "to DIR and exit, for running baseline/_ref/bin/reference_runner by hand or under a profiler")
     ap.add_argument("--study", default=None, choices=["prefill-clocks"],
                     help="prefill-clocks: 40 prompt steps of 2,048 tokens back to back with the clock and the power "
                          "sampled every 20 ms; prints a table and no JSON line")
@@ -387,6 +390,10 @@ def main() -> int:
     if args.impl == "reference":
         if args.gpus != 1:
             print(json.dumps({"impl": "reference", "unavailable": "upstream runs on one GPU only"}))
+            return 0
+        if args.write_model:
+            write_reference_model(args.write_model, args.layers or QWEN3_8B["num_hidden_layers"])
+            print(f"wrote {args.write_model}")
             return 0
         return reference_arm(args)
     if args.gpus != 1:
